@@ -28,6 +28,7 @@ struct Session {
     unsigned long long key = 0;
     std::vector<int> pages;      // KV pages in position order
     std::vector<int> tokens;     // tokens whose K/V sit in the cache (positions 0..size-1)
+    int slot = -1;               // recurrent-state slot (models with stateful mixers), -1 = none
     bool busy = false;
     bool close_pending = false;  // session_close arrived while its request was inside a running step
     long long last_used = 0;
@@ -61,6 +62,7 @@ struct StepMeta {
     // offsets (in ints).  Fixed-size arrays come first; the page table and the per-token arrays
     // are packed behind them at per-step offsets so one H2D copy moves only what the step uses.
     size_t o_ctx, o_qstart, o_rslot, o_rpos0, o_treq, o_tq0, o_lrow, o_temp, o_topk, o_topp, o_seed,
+        o_xstart, o_xpos0, o_xslot,               // every request of the step, decode rows first: first row | position of it | state slot
         o_pt;                                     // fixed
     size_t o_tokens, o_pos, o_rows, upload_ints;  // set by layout_step()
     size_t o_tprefix, o_sampled;                  // device-side work areas (never uploaded)
@@ -74,9 +76,13 @@ static void layout_step(StepMeta& m, int n_req, int max_pages, int T) {
     m.upload_ints = m.o_rows + align4(T);
 }
 
+struct Layered;
+
 struct Engine {
     ft_engine_config cfg;
     ft_weights w;
+    Layered* lay = nullptr;      // non-null: a layered model (ft_engine_create_layered) instead of the Llama field set
+    std::vector<int> free_slots; // recurrent-state slots not owned by a session
     int dev = 0, sms = 148;
     cudaStream_t stream = nullptr;
     std::mutex mu;               // scheduler state; NOT held while a step's kernels run
@@ -156,6 +162,28 @@ struct Engine {
     int waiters = 0;                       // threads inside ft_engine_wait
     bool closing = false;                  // ft_engine_destroy has begun: waiters leave, nobody new comes in
 };
+
+// A layered model inside the engine: the descriptors, the paged latent cache of its attention layers, the state slots
+// of its recurrent layers and the fp32 work buffers of a step.
+struct LayeredLayer {
+    ft_layer_desc d;
+    size_t cache_off = 0;              // floats: this layer's [num_pages][64][kv_rank] block in lat_cache
+    size_t s_off = 0, tail_off = 0;    // floats inside a state slot: S [heads][dim][vdim], tails [channels][conv - 1]
+};
+struct Layered {
+    ft_layered_model m;
+    std::vector<LayeredLayer> layers;
+    float* lat_cache = nullptr;
+    float* state = nullptr;
+    size_t slot_stride = 0;            // floats per state slot
+    int n_stateful = 0;                // layers whose mixer carries state from token to token
+    int ld_proj = 0, top_max = 0;
+    float *hn = nullptr, *proj = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *b4 = nullptr, *beta = nullptr,
+          *mix = nullptr, *act = nullptr, *eout = nullptr, *wts = nullptr, *xlast = nullptr;
+    int *ids = nullptr, *seg = nullptr, *slot_token = nullptr, *slot_pos = nullptr;
+    float* trail = nullptr;            // debug: residual stream after every layer [n_layers][t_max][width]
+    bool trail_on = false;
+};
 constexpr size_t kStepTimes = 4096;
 constexpr int kDefaultPrefillPlanes = 3;      // one fp16 plane x fp16 weight copies in the large prefill GEMMs (measured: DESIGN.md §2)
 constexpr int kGemmTokenTile = 128;             // token tile of the multi-tile projections (gemm_pick_bn)
@@ -233,6 +261,7 @@ static void release_pages_beyond(Engine* e, Session* s, int keep_tokens) {
 
 static void drop_session(Engine* e, Session* s) {
     release_pages_beyond(e, s, 0);
+    if (s->slot >= 0) e->free_slots.push_back(s->slot);
     e->sessions.erase(s->key);
     delete s;
 }
@@ -342,7 +371,10 @@ static int run_gemm(Engine* e, const CUtensorMap& mw, const CUtensorMap* xmaps, 
 //   QKV GEMM [x 1/rms, RoPE, KV append] -> attention -> O GEMM [resid +=, planes = resid*gamma_mlp, ssq]
 //   -> gate/up GEMM [x 1/rms, SwiGLU] -> down GEMM [resid +=, planes = resid*gamma_next, ssq]
 // `xn` planes always hold resid * gamma of the NEXT norm; `ssq` its per-row-tile sums of squares.
+static int forward_layered(Engine* e, const Batch& b);
+
 static int forward(Engine* e, const Batch& b) {
+    if (e->lay) return forward_layered(e, b);
     const ft_engine_config& c = e->cfg;
     StepMeta& m = e->meta;
     int* d = m.d;
@@ -504,6 +536,120 @@ static int forward(Engine* e, const Batch& b) {
     return 0;
 }
 
+// Forward pass of a layered model.  Per layer: ONE projection of the normed input into all the parts that read it
+// (queries, latents or q/k/v, gates, low-rank inner products, residual gates, router logits), the mixer, the experts, and
+// one kernel that updates the residual stream and norms it for the next layer.
+static int forward_layered(Engine* e, const Batch& b) {
+    Layered& L = *e->lay;
+    const ft_layered_model& M = L.m;
+    StepMeta& m = e->meta;
+    int* d = m.d;
+    const int T = b.T, W = M.width, ld = L.ld_proj;
+    cudaStream_t st = e->stream;
+    auto launched = [&](int n = 1) { e->st.kernel_launches += n; };
+    FT_TRY(launch_embed_norm(d + m.o_tokens, M.embed, e->resid, L.hn, T, W, M.eps, L.layers[0].d.norm_gain, st));
+    launched();
+    for (int l = 0; l < M.n_layers; ++l) {
+        const LayeredLayer& ll = L.layers[l];
+        const ft_layer_desc& c = ll.d;
+        {
+            LinearArgs a;
+            a.A = L.hn; a.lda = W; a.W = (const __nv_bfloat16*)c.w_in; a.ldw = W; a.C = L.proj; a.ldc = ld;
+            a.M = T; a.N = c.n_in; a.K = W;
+            FT_TRY(launch_linear(a, T, st));
+            launched();
+        }
+        const float* mixed = nullptr;      // [T][heads * vdim], input of the output projection
+        if (c.mixer == FT_MIXER_LATENT_ATTENTION) {
+            float* cache = L.lat_cache + ll.cache_off;
+            FT_TRY(launch_latent_write(L.proj, ld, c.o_dkv, c.dkv_norm, cache, d + m.o_pos, d + m.o_rows, d + m.o_pt,
+                                       e->max_pages, c.kv_rank, M.eps, T, st));
+            LinearArgs a;                   // queries into latent space, head by head: qlat_h = W_uk_h^T q_h
+            a.A = L.proj + c.o_q; a.lda = ld; a.a_col_stride = c.dim;
+            a.W = (const __nv_bfloat16*)c.w_uk_t; a.w_stride = (long long)c.kv_rank * c.dim; a.ldw = c.dim;
+            a.C = L.b1; a.ldc = c.heads * c.kv_rank; a.c_col_stride = c.kv_rank;
+            a.M = T; a.N = c.kv_rank; a.K = c.dim; a.P = c.heads;
+            FT_TRY(launch_linear(a, T, st));
+            FT_TRY(launch_latent_attn(L.b1, cache, L.proj, ld, c.o_gate, L.b2, d + m.o_pos, d + m.o_rows, d + m.o_pt,
+                                      e->max_pages, c.heads, c.kv_rank, c.scale, T, st));
+            LinearArgs v;                   // values out of latent space: o_h = W_uv_h (sum_j p_j c_j)
+            v.A = L.b2; v.lda = c.heads * c.kv_rank; v.a_col_stride = c.kv_rank;
+            v.W = (const __nv_bfloat16*)c.w_uv; v.w_stride = (long long)c.vdim * c.kv_rank; v.ldw = c.kv_rank;
+            v.C = L.b3; v.ldc = c.heads * c.vdim; v.c_col_stride = c.vdim;
+            v.M = T; v.N = c.vdim; v.K = c.kv_rank; v.P = c.heads;
+            FT_TRY(launch_linear(v, T, st));
+            launched(4);
+            mixed = L.b3;
+        } else {
+            LinearArgs a;                   // second halves of the low-rank decay and gate projections
+            a.A = L.proj + c.o_a1; a.lda = ld; a.W = (const __nv_bfloat16*)c.w_a2; a.ldw = c.rank_a;
+            a.C = L.b1; a.ldc = c.heads * c.dim; a.M = T; a.N = c.heads * c.dim; a.K = c.rank_a;
+            FT_TRY(launch_linear(a, T, st));
+            LinearArgs g;
+            g.A = L.proj + c.o_g1; g.lda = ld; g.W = (const __nv_bfloat16*)c.w_g2; g.ldw = c.rank_g;
+            g.C = L.b2; g.ldc = c.heads * c.vdim; g.M = T; g.N = c.heads * c.vdim; g.K = c.rank_g;
+            FT_TRY(launch_linear(g, T, st));
+            DeltaArgs da;
+            da.proj = L.proj; da.ldp = ld; da.o_q = c.o_q; da.o_beta = c.o_beta;
+            da.conv = c.conv_w; da.araw = L.b1; da.dt_bias = c.dt_bias; da.a_log = c.a_log;
+            da.qkv = L.b3; da.decay = L.b1; da.beta = L.beta; da.o = L.b4;
+            da.state = L.state; da.slot_stride = (long long)L.slot_stride; da.s_off = (long long)ll.s_off;
+            da.tail_off = (long long)ll.tail_off;
+            da.seq_rows = d + m.o_rows; da.req_start = d + m.o_xstart; da.req_pos0 = d + m.o_xpos0;
+            da.req_slot = d + m.o_xslot;
+            da.heads = c.heads; da.kvh = c.kv_heads; da.dim = c.dim; da.vdim = c.vdim; da.taps = c.conv;
+            FT_TRY(launch_delta(da, L.b2, c.out_norm, M.eps, T, b.n_req, st));
+            launched(6);
+            mixed = L.b4;
+        }
+        {
+            LinearArgs a;
+            a.A = mixed; a.lda = c.heads * c.vdim; a.W = (const __nv_bfloat16*)c.w_o; a.ldw = c.heads * c.vdim;
+            a.C = L.mix; a.ldc = W; a.M = T; a.N = W; a.K = c.heads * c.vdim;
+            FT_TRY(launch_linear(a, T, st));
+            launched();
+        }
+        int top = 0;
+        if (c.ff_kind == FT_FF_MOE) {
+            top = c.top;
+            FT_TRY(launch_route(L.proj, ld, c.o_router, c.experts, c.top, c.groups, c.keep, L.ids, L.wts, L.seg,
+                                L.slot_token, L.slot_pos, T, st));
+            LinearArgs gu;                  // gate and up of every (token, choice) pair, grouped by expert
+            gu.A = L.hn; gu.a_rows = L.slot_token; gu.lda = W; gu.W = (const __nv_bfloat16*)c.w_gu;
+            gu.w_stride = (long long)2 * c.ff * W; gu.ldw = W; gu.C = L.act; gu.ldc = c.ff; gu.seg = L.seg;
+            gu.N = 2 * c.ff; gu.K = W; gu.P = c.experts; gu.epi = LIN_SWIGLU_PAIR;
+            FT_TRY(launch_linear(gu, T * top, st));
+            LinearArgs dn;
+            dn.A = L.act; dn.lda = c.ff; dn.W = (const __nv_bfloat16*)c.w_down; dn.w_stride = (long long)W * c.ff;
+            dn.ldw = c.ff; dn.C = L.eout; dn.ldc = W; dn.seg = L.seg; dn.N = W; dn.K = c.ff; dn.P = c.experts;
+            FT_TRY(launch_linear(dn, T * top, st));
+            launched(4);
+        }
+        const float gain_next = l + 1 < M.n_layers ? L.layers[l + 1].d.norm_gain : M.final_norm_gain;
+        FT_TRY(launch_combine_norm(e->resid, L.hn, L.proj, ld, c.o_rg1, c.o_rg2, c.rg_bias, L.mix, L.eout, L.wts,
+                                   L.slot_pos, top, T, W, M.eps, gain_next, st));
+        launched();
+        if (L.trail_on && L.trail)
+            FT_CHECK_CUDA(cudaMemcpyAsync(L.trail + (size_t)l * e->t_max * W, e->resid, (size_t)T * W * 4,
+                                          cudaMemcpyDeviceToDevice, st));
+    }
+    if (b.n_logit_rows > 0) {
+        const float* x = L.hn;
+        if (!b.logit_rows_identity) {
+            FT_TRY(launch_gather_rows(L.hn, d + m.o_lrow, L.xlast, b.n_logit_rows, W, st));
+            launched();
+            x = L.xlast;
+        }
+        LinearArgs a;
+        a.A = x; a.lda = W; a.W = (const __nv_bfloat16*)M.head; a.ldw = W; a.C = e->logits; a.ldc = M.vocab;
+        a.M = b.n_logit_rows; a.N = M.vocab; a.K = W;
+        if (M.logit_softcap > 0.f) { a.epi = LIN_SOFTCAP; a.cap = M.logit_softcap; }
+        FT_TRY(launch_linear(a, b.n_logit_rows, st));
+        launched();
+    }
+    return 0;
+}
+
 static int upload_meta(Engine* e) {
     FT_CHECK_CUDA(cudaMemcpyAsync(e->meta.d, e->meta.h, e->meta.upload_ints * sizeof(int),
                                   cudaMemcpyHostToDevice, e->stream));
@@ -516,6 +662,67 @@ static unsigned long long mix64(unsigned long long x) {
     x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
     x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
     return x ^ (x >> 31);
+}
+
+// ------------------------------------------------------------------ batch builder
+// What a step runs for one sequence: its next `n` tokens, the first of them at position pos0.
+struct Portion { Session* sess; const int* toks; int n; int pos0; };
+
+// Fills the step's metadata block: decode rows (one token each) first, then prompt portions.  Shared by the scheduler's
+// steps, ft_engine_feed and the debug hooks, so every path lays a batch out the same way.  Returns the summed context
+// lengths of the decode rows.
+static long long fill_batch(Engine* e, const std::vector<Portion>& dec, const std::vector<Portion>& pre, Batch& b) {
+    StepMeta& m = e->meta;
+    int* h = m.h;
+    b.n_decode = (int)dec.size();
+    b.n_prefill_req = (int)pre.size();
+    b.n_req = b.n_decode + b.n_prefill_req;
+    {
+        int total = b.n_decode;
+        for (const Portion& p : pre) total += p.n;
+        layout_step(m, b.n_req, e->max_pages, total);
+    }
+    int row = 0;
+    long long ctx_sum = 0;
+    for (int i = 0; i < b.n_decode; ++i, ++row) {
+        const Portion& p = dec[i];
+        h[m.o_tokens + row] = p.toks[0];
+        h[m.o_pos + row] = p.pos0;
+        h[m.o_rows + row] = i;
+        h[m.o_ctx + i] = p.pos0 + 1;
+        ctx_sum += p.pos0 + 1;
+        for (size_t k = 0; k < p.sess->pages.size(); ++k) h[m.o_pt + (size_t)i * e->max_pages + k] = p.sess->pages[k];
+        h[m.o_xstart + i] = row;
+        h[m.o_xpos0 + i] = p.pos0;
+        h[m.o_xslot + i] = p.sess->slot;
+    }
+    int tiles = 0;
+    h[m.o_qstart] = row;
+    for (int j = 0; j < b.n_prefill_req; ++j) {
+        const Portion& p = pre[j];
+        const int pt_row = b.n_decode + j;
+        h[m.o_xstart + pt_row] = row;
+        h[m.o_xpos0 + pt_row] = p.pos0;
+        h[m.o_xslot + pt_row] = p.sess->slot;
+        for (int k = 0; k < p.n; ++k, ++row) {
+            h[m.o_tokens + row] = p.toks[k];
+            h[m.o_pos + row] = p.pos0 + k;
+            h[m.o_rows + row] = pt_row;
+        }
+        h[m.o_qstart + j + 1] = row;
+        h[m.o_rslot + j] = pt_row;
+        h[m.o_rpos0 + j] = p.pos0;
+        for (size_t k = 0; k < p.sess->pages.size(); ++k)
+            h[m.o_pt + (size_t)pt_row * e->max_pages + k] = p.sess->pages[k];
+        for (int q0 = 0; q0 < p.n; q0 += 64, ++tiles) {
+            h[m.o_treq + tiles] = j;
+            h[m.o_tq0 + tiles] = q0;
+        }
+    }
+    h[m.o_xstart + b.n_req] = row;
+    b.T = row;
+    b.n_tiles = tiles;
+    return ctx_sum;
 }
 
 // ------------------------------------------------------------------ one scheduler step
@@ -589,62 +796,28 @@ static int engine_step(Engine* e, std::unique_lock<std::mutex>& lk) {
             ++i;
         }
     }
-    b.n_decode = (int)dec.size();
-    b.n_prefill_req = (int)pre.size();
-    b.n_req = b.n_decode + b.n_prefill_req;
-    if (b.n_req == 0) return 0;
-    {
-        int total = b.n_decode;
-        for (int len : pre_len) total += len;
-        layout_step(m, b.n_req, e->max_pages, total);
-    }
-
-    int row = 0, lrow = 0;
-    long long ctx_sum = 0;
-    for (int i = 0; i < b.n_decode; ++i, ++row) {
-        Request* r = dec[i];
-        Session* s = r->sess;
-        const int pos = (int)s->tokens.size();
-        h[m.o_tokens + row] = r->last_token;
-        h[m.o_pos + row] = pos;
-        h[m.o_rows + row] = i;
-        h[m.o_ctx + i] = pos + 1;
-        ctx_sum += pos + 1;
-        for (size_t p = 0; p < s->pages.size(); ++p) h[m.o_pt + (size_t)i * e->max_pages + p] = s->pages[p];
-        h[m.o_lrow + lrow] = row;
-        r->logits_row = lrow++;
-    }
+    if (dec.empty() && pre.empty()) return 0;
+    std::vector<Portion> dec_p, pre_p;
+    for (Request* r : dec) dec_p.push_back({r->sess, &r->last_token, 1, (int)r->sess->tokens.size()});
+    for (size_t j = 0; j < pre.size(); ++j)
+        pre_p.push_back({pre[j]->sess, pre[j]->prompt.data() + pre[j]->prefill_pos, pre_len[j], pre[j]->prefill_pos});
+    const long long ctx_sum = fill_batch(e, dec_p, pre_p, b);
     e->prof_ctx_sum = ctx_sum;
     e->st.decode_ctx_tokens += ctx_sum;
-    int tiles = 0;
-    h[m.o_qstart] = row;
+    // rows whose logits are sampled: every decode row, and the last row of a prompt that is complete
+    int lrow = 0;
+    for (int i = 0; i < b.n_decode; ++i) {
+        h[m.o_lrow + lrow] = i;
+        dec[i]->logits_row = lrow++;
+    }
     for (int j = 0; j < b.n_prefill_req; ++j) {
         Request* r = pre[j];
-        Session* s = r->sess;
-        const int pt_row = b.n_decode + j;
-        const int pos0 = r->prefill_pos;
-        for (int k = 0; k < pre_len[j]; ++k, ++row) {
-            h[m.o_tokens + row] = r->prompt[pos0 + k];
-            h[m.o_pos + row] = pos0 + k;
-            h[m.o_rows + row] = pt_row;
-        }
-        h[m.o_qstart + j + 1] = row;
-        h[m.o_rslot + j] = pt_row;
-        h[m.o_rpos0 + j] = pos0;
-        for (size_t p = 0; p < s->pages.size(); ++p)
-            h[m.o_pt + (size_t)pt_row * e->max_pages + p] = s->pages[p];
-        for (int q0 = 0; q0 < pre_len[j]; q0 += 64, ++tiles) {
-            h[m.o_treq + tiles] = j;
-            h[m.o_tq0 + tiles] = q0;
-        }
         r->logits_row = -1;
-        if (pos0 + pre_len[j] == (int)r->prompt.size()) {      // prompt complete: sample from last row
-            h[m.o_lrow + lrow] = row - 1;
+        if (r->prefill_pos + pre_len[j] == (int)r->prompt.size()) {
+            h[m.o_lrow + lrow] = h[m.o_qstart + j + 1] - 1;
             r->logits_row = lrow++;
         }
     }
-    b.T = row;
-    b.n_tiles = tiles;
     b.n_logit_rows = lrow;
     b.logit_rows_identity = lrow == b.T && b.n_prefill_req == 0;      // pure decode: row i wants logits row i
     // sampling parameters per logit row
@@ -762,8 +935,53 @@ static int engine_step(Engine* e, std::unique_lock<std::mutex>& lk) {
     return produced;
 }
 
+// The pinned + device block of per-step metadata (layout: StepMeta).
+static int init_meta(Engine* e, size_t rows_last) {
+    const ft_engine_config& c = e->cfg;
+    const size_t T = e->t_max;
+    StepMeta& m = e->meta;
+    size_t o = 0;
+    auto take = [&](size_t n) { size_t r = o; o += align4(n); return r; };
+    const size_t R = e->r_max, LR = rows_last;
+    const size_t max_tiles = T / 64 + R + 1;
+    m.o_ctx = take(R); m.o_qstart = take(R + 1); m.o_rslot = take(R); m.o_rpos0 = take(R);
+    m.o_treq = take(max_tiles); m.o_tq0 = take(max_tiles);
+    m.o_lrow = take(LR); m.o_temp = take(LR); m.o_topk = take(LR); m.o_topp = take(LR);
+    m.o_seed = take(2 * LR);
+    m.o_xstart = take(R + 1); m.o_xpos0 = take(R); m.o_xslot = take(R);
+    m.o_pt = take(0);
+    o += align4(R * e->max_pages) + 3 * align4(T);      // page table + tokens | positions | rows
+    m.o_tprefix = take(R + 1);
+    m.o_sampled = take(LR);
+    m.ints = o;
+    layout_step(m, (int)R, e->max_pages, (int)T);
+    FT_CHECK_CUDA(cudaMallocHost(&m.h, o * sizeof(int)));
+    FT_CHECK_CUDA(cudaMalloc(&m.d, o * sizeof(int)));
+    memset(m.h, 0, o * sizeof(int));
+    FT_CHECK_CUDA(cudaMemsetAsync(m.d, 0, o * sizeof(int), e->stream));
+
+    return 0;
+}
+
+static int init_events_and_pages(Engine* e) {
+    const ft_engine_config& c = e->cfg;
+    e->prof_ev.resize(2 * (size_t)std::max(e->cfg.layers, 1));
+    for (auto& ev : e->prof_ev) FT_CHECK_CUDA(cudaEventCreate(&ev));
+    FT_CHECK_CUDA(cudaEventCreate(&e->t0));
+    FT_CHECK_CUDA(cudaEventCreate(&e->t1));
+    FT_CHECK_CUDA(cudaEventCreate(&e->s0));
+    FT_CHECK_CUDA(cudaEventCreate(&e->s1));
+    e->free_pages.reserve(c.num_pages);
+    for (int p = c.num_pages - 1; p >= 0; --p) e->free_pages.push_back(p);
+    e->st.total_pages = c.num_pages;
+    return 0;
+}
+
+static int engine_init_layered(Engine* e);
+
 // ------------------------------------------------------------------ construction
 static int engine_init(Engine* e) {
+    if (e->lay) return engine_init_layered(e);
     const ft_engine_config& c = e->cfg;
     FT_REQUIRE(c.head_dim == 64 || c.head_dim == 128, "engine: head_dim %d not supported", c.head_dim);
     FT_REQUIRE(c.n_q_heads % c.n_kv_heads == 0 && c.n_q_heads / c.n_kv_heads <= 8,
@@ -851,26 +1069,7 @@ static int engine_init(Engine* e) {
                              attn_decode_scratch_floats(e->r_max, c.n_kv_heads, e->group, c.head_dim,
                                                         e->attn_ctas) * 4));
 
-    // step metadata block
-    StepMeta& m = e->meta;
-    size_t o = 0;
-    auto take = [&](size_t n) { size_t r = o; o += align4(n); return r; };
-    const size_t R = e->r_max, LR = rows_last;
-    const size_t max_tiles = T / 64 + R + 1;
-    m.o_ctx = take(R); m.o_qstart = take(R + 1); m.o_rslot = take(R); m.o_rpos0 = take(R);
-    m.o_treq = take(max_tiles); m.o_tq0 = take(max_tiles);
-    m.o_lrow = take(LR); m.o_temp = take(LR); m.o_topk = take(LR); m.o_topp = take(LR);
-    m.o_seed = take(2 * LR);
-    m.o_pt = take(0);
-    o += align4(R * e->max_pages) + 3 * align4(T);      // page table + tokens | positions | rows
-    m.o_tprefix = take(R + 1);
-    m.o_sampled = take(LR);
-    m.ints = o;
-    layout_step(m, (int)R, e->max_pages, (int)T);
-    FT_CHECK_CUDA(cudaMallocHost(&m.h, o * sizeof(int)));
-    FT_CHECK_CUDA(cudaMalloc(&m.d, o * sizeof(int)));
-    memset(m.h, 0, o * sizeof(int));
-    FT_CHECK_CUDA(cudaMemsetAsync(m.d, 0, o * sizeof(int), e->stream));
+    FT_TRY(init_meta(e, rows_last));
 
     // tensor maps
     const size_t L = c.layers;
@@ -923,15 +1122,113 @@ static int engine_init(Engine* e) {
             FT_TRY(make_tmap_bf16_k64(&e->m16_act[i], e->x16_act, (int)T, c.ffn, boxes[i]));
         }
     }
-    e->prof_ev.resize(2 * L);
-    for (auto& ev : e->prof_ev) FT_CHECK_CUDA(cudaEventCreate(&ev));
-    FT_CHECK_CUDA(cudaEventCreate(&e->t0));
-    FT_CHECK_CUDA(cudaEventCreate(&e->t1));
-    FT_CHECK_CUDA(cudaEventCreate(&e->s0));
-    FT_CHECK_CUDA(cudaEventCreate(&e->s1));
-    e->free_pages.reserve(c.num_pages);
-    for (int p = c.num_pages - 1; p >= 0; --p) e->free_pages.push_back(p);
-    e->st.total_pages = c.num_pages;
+    FT_TRY(init_events_and_pages(e));
+    FT_CHECK_CUDA(cudaStreamSynchronize(e->stream));
+    return 0;
+}
+
+static int engine_init_layered(Engine* e) {
+    const ft_engine_config& c = e->cfg;
+    Layered& L = *e->lay;
+    const ft_layered_model& M = L.m;
+    FT_REQUIRE(M.width >= 1 && M.vocab >= 1 && M.n_layers >= 1, "engine: a layered model needs width, vocab and layers");
+    FT_REQUIRE(c.max_batch >= 1 && c.max_batched_tokens >= c.max_batch, "engine: bad batch limits");
+    FT_REQUIRE(c.max_context >= 1 && c.num_pages >= 1, "engine: bad context/page limits");
+    FT_CHECK_CUDA(cudaGetDevice(&e->dev));
+    FT_CHECK_CUDA(cudaDeviceGetAttribute(&e->sms, cudaDevAttrMultiProcessorCount, e->dev));
+    int cc_major = 0;
+    FT_CHECK_CUDA(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, e->dev));
+    FT_REQUIRE(cc_major == 10, "engine: needs an sm_100 GPU (found compute capability %d.x)", cc_major);
+    FT_CHECK_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+    e->max_pages = ceil_div(c.max_context, kKvTile);
+    e->t_max = c.max_batched_tokens;
+    e->r_max = c.max_batch;
+    e->logit_rows = std::max(c.max_batch, c.debug_logit_rows);
+    e->pdl = false;
+    e->tp = 1;
+    e->vocab_local = M.vocab;
+    e->decode_prefill_cap = c.decode_prefill_cap == 0 ? kDefaultDecodePrefillCap : c.decode_prefill_cap < 0 ? 0 : c.decode_prefill_cap;
+
+    // sizes over all layers; places of each layer in the latent cache and in a state slot
+    size_t cache_floats = 0, buf = 1, act_cols = 1;
+    int n_in_max = 1, top_max = 1, heads_max = 1;
+    for (int l = 0; l < M.n_layers; ++l) {
+        LayeredLayer& ll = L.layers[l];
+        const ft_layer_desc& d = ll.d;
+        FT_REQUIRE(d.heads >= 1 && d.dim >= 1 && d.vdim >= 1 && d.n_in >= 1 && d.w_in && d.w_o && d.rg_bias && d.o_rg1 >= 0,
+                   "engine: layer %d is incomplete", l);
+        n_in_max = std::max(n_in_max, d.n_in);
+        heads_max = std::max(heads_max, d.heads);
+        buf = std::max(buf, (size_t)d.heads * d.vdim);
+        if (d.mixer == FT_MIXER_LATENT_ATTENTION) {
+            FT_REQUIRE(d.kv_rank >= 1 && d.w_uk_t && d.w_uv && d.dkv_norm && d.o_q >= 0 && d.o_dkv >= 0 && d.o_gate >= 0,
+                       "engine: latent-attention layer %d is incomplete", l);
+            ll.cache_off = cache_floats;
+            cache_floats += (size_t)c.num_pages * kKvTile * d.kv_rank;
+            buf = std::max(buf, (size_t)d.heads * d.kv_rank);
+        } else if (d.mixer == FT_MIXER_CHANNEL_DELTA) {
+            FT_REQUIRE(d.kv_heads >= 1 && d.heads % d.kv_heads == 0 && d.conv >= 1 && d.rank_a >= 1 && d.rank_g >= 1 &&
+                           d.conv_w && d.w_a2 && d.w_g2 && d.dt_bias && d.a_log && d.out_norm && d.o_q >= 0 &&
+                           d.o_beta >= 0 && d.o_a1 >= 0 && d.o_g1 >= 0,
+                       "engine: channel-delta layer %d is incomplete", l);
+            const size_t ch = (size_t)2 * d.kv_heads * d.dim + (size_t)d.heads * d.vdim;
+            ll.s_off = L.slot_stride;
+            L.slot_stride += (size_t)d.heads * d.dim * d.vdim;
+            ll.tail_off = L.slot_stride;
+            L.slot_stride += ch * (size_t)std::max(d.conv - 1, 0);
+            L.slot_stride = (L.slot_stride + 3) & ~size_t(3);
+            L.n_stateful++;
+            buf = std::max(buf, std::max(ch, (size_t)d.heads * d.dim));
+        } else {
+            FT_REQUIRE(false, "engine: layer %d has an unknown mixer %d", l, d.mixer);
+        }
+        if (d.ff_kind == FT_FF_MOE) {
+            FT_REQUIRE(d.experts >= 1 && d.top >= 1 && d.ff >= 1 && d.w_gu && d.w_down && d.o_router >= 0 && d.o_rg2 >= 0,
+                       "engine: mixture-of-experts layer %d is incomplete", l);
+            top_max = std::max(top_max, d.top);
+            act_cols = std::max(act_cols, (size_t)d.ff);
+        } else {
+            FT_REQUIRE(d.ff_kind == FT_FF_NONE, "engine: layer %d has an unknown feed-forward %d", l, d.ff_kind);
+        }
+    }
+    L.ld_proj = (n_in_max + 3) & ~3;
+    L.top_max = top_max;
+    const size_t T = e->t_max, W = M.width;
+    auto alloc = [&](void* pp, size_t bytes) -> int {
+        void** p = reinterpret_cast<void**>(pp);
+        FT_CHECK_CUDA(cudaMalloc(p, std::max<size_t>(bytes, 16)));
+        FT_CHECK_CUDA(cudaMemsetAsync(*p, 0, std::max<size_t>(bytes, 16), e->stream));
+        return 0;
+    };
+    FT_TRY(alloc(&L.lat_cache, cache_floats * 4));
+    FT_TRY(alloc(&L.state, L.slot_stride * (size_t)c.max_sessions * 4));
+    FT_TRY(alloc(&e->resid, T * W * 4));
+    FT_TRY(alloc(&L.hn, T * W * 4));
+    FT_TRY(alloc(&L.proj, T * L.ld_proj * 4));
+    FT_TRY(alloc(&L.b1, T * buf * 4));
+    FT_TRY(alloc(&L.b2, T * buf * 4));
+    FT_TRY(alloc(&L.b3, T * buf * 4));
+    FT_TRY(alloc(&L.b4, T * buf * 4));
+    FT_TRY(alloc(&L.beta, T * heads_max * 4));
+    FT_TRY(alloc(&L.mix, T * W * 4));
+    FT_TRY(alloc(&L.act, T * top_max * act_cols * 4));
+    FT_TRY(alloc(&L.eout, T * top_max * W * 4));
+    FT_TRY(alloc(&L.wts, T * top_max * 4));
+    FT_TRY(alloc(&L.ids, T * top_max * 4));
+    FT_TRY(alloc(&L.slot_token, T * top_max * 4));
+    FT_TRY(alloc(&L.slot_pos, T * top_max * 4));
+    {
+        int e_max = 1;
+        for (const LayeredLayer& ll : L.layers) e_max = std::max(e_max, ll.d.experts);
+        FT_TRY(alloc(&L.seg, (size_t)(e_max + 1) * 4));
+    }
+    const size_t rows_last = std::max<size_t>(e->logit_rows, 256);
+    e->rows_last = (int)rows_last;
+    FT_TRY(alloc(&L.xlast, rows_last * W * 4));
+    FT_TRY(alloc(&e->logits, (size_t)e->logit_rows * M.vocab * 4));
+    for (int sl = c.max_sessions - 1; sl >= 0; --sl) e->free_slots.push_back(sl);
+    FT_TRY(init_meta(e, rows_last));
+    FT_TRY(init_events_and_pages(e));
     FT_CHECK_CUDA(cudaStreamSynchronize(e->stream));
     return 0;
 }
@@ -947,6 +1244,14 @@ static void engine_free(Engine* e) {
     cudaFree(e->attn_scratch); cudaFree(e->meta.d);
     cudaFree(e->w16_qkv); cudaFree(e->w16_o); cudaFree(e->w16_gu); cudaFree(e->w16_d);
     cudaFree(e->x16_xn); cudaFree(e->x16_attn); cudaFree(e->x16_act);
+    if (e->lay) {
+        Layered& L = *e->lay;
+        cudaFree(L.lat_cache); cudaFree(L.state); cudaFree(L.hn); cudaFree(L.proj); cudaFree(L.b1); cudaFree(L.b2);
+        cudaFree(L.b3); cudaFree(L.b4); cudaFree(L.beta); cudaFree(L.mix); cudaFree(L.act); cudaFree(L.eout);
+        cudaFree(L.wts); cudaFree(L.xlast); cudaFree(L.ids); cudaFree(L.seg); cudaFree(L.slot_token);
+        cudaFree(L.slot_pos); cudaFree(L.trail);
+        delete e->lay;
+    }
     if (e->meta.h) cudaFreeHost(e->meta.h);
     for (auto ev : e->prof_ev) if (ev) cudaEventDestroy(ev);
     if (e->t0) cudaEventDestroy(e->t0);
@@ -973,6 +1278,175 @@ extern "C" ft_engine* ft_engine_create(const ft_engine_config* cfg, const ft_wei
     return reinterpret_cast<ft_engine*>(e);
 }
 
+extern "C" ft_engine* ft_engine_create_layered(const ft_engine_config* cfg, const ft_layered_model* model) {
+    if (!cfg || !model || !model->layers || model->n_layers < 1) {
+        set_last_error("ft_engine_create_layered: null argument");
+        return nullptr;
+    }
+    Engine* e = new (std::nothrow) Engine();
+    if (!e) { set_last_error("ft_engine_create_layered: out of host memory"); return nullptr; }
+    e->cfg = *cfg;
+    e->w = ft_weights{};
+    e->lay = new Layered();
+    e->lay->m = *model;
+    e->lay->layers.resize(model->n_layers);
+    for (int l = 0; l < model->n_layers; ++l) e->lay->layers[l].d = model->layers[l];
+    e->lay->m.layers = nullptr;
+    e->cfg.hidden = model->width;
+    e->cfg.vocab = model->vocab;
+    e->cfg.layers = model->n_layers;
+    if (e->cfg.max_sessions < e->cfg.max_batch) e->cfg.max_sessions = e->cfg.max_batch * 4;
+    if (engine_init(e) != 0) { engine_free(e); return nullptr; }
+    return reinterpret_cast<ft_engine*>(e);
+}
+
+static bool runnable(const Engine* e);
+
+// A session for `key`, made if there is none: the stalest idle session gives way when the table (or, for models with
+// recurrent layers, the state slots) is full.  Under e->mu.
+static Session* session_for(Engine* e, unsigned long long key, const char* who) {
+    auto it = e->sessions.find(key);
+    if (it != e->sessions.end()) return it->second;
+    const bool need_slot = e->lay && e->lay->n_stateful > 0;
+    if ((int)e->sessions.size() >= e->cfg.max_sessions || (need_slot && e->free_slots.empty())) {
+        Session* victim = nullptr;
+        for (auto& kv : e->sessions)
+            if (!kv.second->busy && (!victim || kv.second->last_used < victim->last_used)) victim = kv.second;
+        if (!victim) {
+            set_last_error("%s: all %d sessions are busy", who, e->cfg.max_sessions);
+            return nullptr;
+        }
+        for (auto& kv : e->requests)
+            if (kv.second->sess == victim) kv.second->sess = nullptr;
+        drop_session(e, victim);
+    }
+    Session* s = new Session();
+    s->key = key;
+    if (need_slot) {
+        s->slot = e->free_slots.back();
+        e->free_slots.pop_back();
+    }
+    e->sessions[key] = s;
+    return s;
+}
+
+extern "C" int ft_engine_feed(ft_engine* h, int n_entries, const unsigned long long* keys, const int* counts,
+                              const int* tokens, int n_want, const int* want_rows, float* logits_out) {
+    Engine* e = reinterpret_cast<Engine*>(h);
+    FT_REQUIRE(e && n_entries >= 1 && keys && counts && tokens && n_want >= 0, "ft_engine_feed: bad arguments");
+    FT_REQUIRE(n_want == 0 || (want_rows && logits_out), "ft_engine_feed: wanted rows without a place for them");
+    FT_REQUIRE(n_entries <= e->r_max, "ft_engine_feed: %d entries exceed max_batch %d", n_entries, e->r_max);
+    FT_REQUIRE(n_want <= e->logit_rows, "ft_engine_feed: %d wanted rows exceed debug_logit_rows %d", n_want, e->logit_rows);
+    std::lock_guard<std::mutex> sk(e->step_mu);
+    std::lock_guard<std::mutex> dk(g_device_step_mu[e->dev % kMaxDevices]);
+    DeviceGuard dg(e->dev);
+    std::unique_lock<std::mutex> lk(e->mu);
+    FT_REQUIRE(!e->loop_on && runnable(e) == false, "ft_engine_feed: the engine has requests of its own in flight");
+    int total = 0;
+    for (int i = 0; i < n_entries; ++i) {
+        FT_REQUIRE(counts[i] >= 1, "ft_engine_feed: entry %d is empty", i);
+        for (int j = 0; j < i; ++j) FT_REQUIRE(keys[i] != keys[j], "ft_engine_feed: session %llu appears twice", keys[i]);
+        total += counts[i];
+    }
+    FT_REQUIRE(total <= e->t_max, "ft_engine_feed: %d tokens exceed max_batched_tokens %d", total, e->t_max);
+    for (int i = 0; i < total; ++i)
+        FT_REQUIRE(tokens[i] >= 0 && tokens[i] < e->cfg.vocab, "ft_engine_feed: token %d out of range at %d", tokens[i], i);
+    for (int i = 0; i < n_want; ++i)
+        FT_REQUIRE(want_rows[i] >= 0 && want_rows[i] < total, "ft_engine_feed: wanted row %d out of range", want_rows[i]);
+    // sessions and pages first (a session being made may evict an idle one, never one of this step)
+    std::vector<Session*> sess(n_entries);
+    for (int i = 0; i < n_entries; ++i) {
+        Session* s = session_for(e, keys[i], "ft_engine_feed");
+        if (!s) return -2;
+        FT_REQUIRE(!s->busy, "ft_engine_feed: session %llu has a generation in flight", keys[i]);
+        s->busy = true;                      // not a candidate for eviction while the step is put together
+        s->last_used = ++e->clock;
+        sess[i] = s;
+    }
+    int rc = 0;
+    for (int i = 0; i < n_entries && !rc; ++i) {
+        const int after = (int)sess[i]->tokens.size() + counts[i];
+        if (after > e->cfg.max_context) { set_last_error("ft_engine_feed: session %llu would pass the %d-token context window", keys[i], e->cfg.max_context); rc = -2; }
+        else if (!ensure_pages(e, sess[i], after)) { set_last_error("ft_engine_feed: out of cache pages"); rc = -3; }
+    }
+    // decode rows first, then prompt portions; `place` = first row of entry i in the batch
+    std::vector<Portion> dec, pre;
+    std::vector<int> place(n_entries, 0), first(n_entries, 0);
+    if (!rc) {
+        int off = 0;
+        for (int i = 0; i < n_entries; ++i) { first[i] = off; off += counts[i]; }
+        int row = 0;
+        for (int i = 0; i < n_entries; ++i)
+            if (counts[i] == 1 && !sess[i]->tokens.empty()) {
+                dec.push_back({sess[i], tokens + first[i], 1, (int)sess[i]->tokens.size()});
+                place[i] = row++;
+            }
+        for (int i = 0; i < n_entries; ++i)
+            if (!(counts[i] == 1 && !sess[i]->tokens.empty())) {
+                pre.push_back({sess[i], tokens + first[i], counts[i], (int)sess[i]->tokens.size()});
+                place[i] = row;
+                row += counts[i];
+            }
+        Batch b;
+        fill_batch(e, dec, pre, b);
+        StepMeta& m = e->meta;
+        for (int i = 0; i < n_want; ++i) {
+            int en = n_entries - 1;
+            while (first[en] > want_rows[i]) --en;
+            m.h[m.o_lrow + i] = place[en] + (want_rows[i] - first[en]);
+        }
+        b.n_logit_rows = n_want;
+        b.logit_rows_identity = false;
+        rc = upload_meta(e);
+        if (!rc) rc = forward(e, b);
+        if (!rc && n_want > 0 &&
+            cudaMemcpyAsync(logits_out, e->logits, (size_t)n_want * e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream) != cudaSuccess) {
+            set_last_error("ft_engine_feed: logits copy failed");
+            rc = -1;
+        }
+        if (!rc) {
+            const cudaError_t se = cudaStreamSynchronize(e->stream);
+            if (se != cudaSuccess) { set_last_error("ft_engine_feed: %s", cudaGetErrorString(se)); rc = -1; }
+        }
+        if (!rc) {
+            for (int i = 0; i < n_entries; ++i)
+                sess[i]->tokens.insert(sess[i]->tokens.end(), tokens + first[i], tokens + first[i] + counts[i]);
+            e->st.steps++;
+            e->st.prefill_tokens += total - (long long)dec.size();
+            e->st.decode_tokens += (long long)dec.size();
+            if (!dec.empty()) e->st.decode_steps++;
+            e->st.last_batch = n_entries;
+        }
+    }
+    for (int i = 0; i < n_entries; ++i) sess[i]->busy = false;
+    return rc;
+}
+
+extern "C" int ft_engine_debug_trail(ft_engine* h, int on) {
+    Engine* e = reinterpret_cast<Engine*>(h);
+    FT_REQUIRE(e && e->lay, "ft_engine_debug_trail: not a layered engine");
+    std::lock_guard<std::mutex> sk(e->step_mu);
+    DeviceGuard dg(e->dev);
+    Layered& L = *e->lay;
+    if (on && !L.trail) FT_CHECK_CUDA(cudaMalloc(&L.trail, (size_t)L.m.n_layers * e->t_max * L.m.width * 4));
+    L.trail_on = on != 0;
+    return 0;
+}
+
+extern "C" int ft_engine_debug_read_trail(ft_engine* h, float* host_out, int rows) {
+    Engine* e = reinterpret_cast<Engine*>(h);
+    FT_REQUIRE(e && e->lay && host_out && rows >= 1 && rows <= e->t_max, "ft_engine_debug_read_trail: bad arguments");
+    std::lock_guard<std::mutex> sk(e->step_mu);
+    DeviceGuard dg(e->dev);
+    Layered& L = *e->lay;
+    FT_REQUIRE(L.trail, "ft_engine_debug_read_trail: the trail is off");
+    const size_t W = L.m.width;
+    for (int l = 0; l < L.m.n_layers; ++l)
+        FT_CHECK_CUDA(cudaMemcpy(host_out + (size_t)l * rows * W, L.trail + (size_t)l * e->t_max * W, (size_t)rows * W * 4,
+                                 cudaMemcpyDeviceToHost));
+    return 0;
+}
+
 extern "C" void ft_engine_destroy(ft_engine* h) {
     if (!h) return;
     Engine* e = reinterpret_cast<Engine*>(h);
@@ -997,27 +1471,15 @@ extern "C" long long ft_engine_submit(ft_engine* h, unsigned long long key, cons
     for (int i = 0; i < n; ++i)
         FT_REQUIRE(tokens[i] >= 0 && tokens[i] < e->cfg.vocab, "ft_engine_submit: token %d out of range at %d", tokens[i], i);
     std::lock_guard<std::mutex> lk(e->mu);
-    Session* s = nullptr;
-    auto it = e->sessions.find(key);
-    if (it != e->sessions.end()) {
-        s = it->second;
-        FT_REQUIRE(!s->busy, "ft_engine_submit: session %llu already has a generation in flight", key);
-    } else {
-        if ((int)e->sessions.size() >= e->cfg.max_sessions) {      // drop the stalest idle session
-            Session* victim = nullptr;
-            for (auto& kv : e->sessions)
-                if (!kv.second->busy && (!victim || kv.second->last_used < victim->last_used)) victim = kv.second;
-            FT_REQUIRE(victim, "ft_engine_submit: all %d sessions are busy", e->cfg.max_sessions);
-            drop_session(e, victim);
-        }
-        s = new Session();
-        s->key = key;
-        e->sessions[key] = s;
-    }
+    Session* s = session_for(e, key, "ft_engine_submit");
+    if (!s) return -2;
+    FT_REQUIRE(!s->busy, "ft_engine_submit: session %llu already has a generation in flight", key);
     // longest common prefix with the cached conversation; at least one token must run
     int lcp = 0;
     const int lim = std::min((int)s->tokens.size(), n - 1);
     while (lcp < lim && s->tokens[lcp] == tokens[lcp]) ++lcp;
+    // a recurrent state stands at the END of what it has seen: it can be continued, not rewound
+    if (e->lay && e->lay->n_stateful > 0 && lcp != (int)s->tokens.size()) lcp = 0;
     release_pages_beyond(e, s, lcp);
     e->st.prefix_hit_tokens += lcp;
     s->busy = true;
@@ -1345,28 +1807,25 @@ extern "C" int ft_debug_prefill_logits(ft_engine* h, const int* tokens, int n, i
                e->logit_rows, e->t_max);
     FT_REQUIRE(n + 1 <= e->cfg.max_context, "ft_debug_prefill_logits: too long");
     Session tmp;
-    if (!ensure_pages(e, &tmp, n)) { set_last_error("ft_debug_prefill_logits: out of KV pages"); return -3; }
+    if (e->lay && e->lay->n_stateful > 0) {
+        FT_REQUIRE(!e->free_slots.empty(), "ft_debug_prefill_logits: no free state slot");
+        tmp.slot = e->free_slots.back();
+        e->free_slots.pop_back();
+    }
+    if (!ensure_pages(e, &tmp, n)) {
+        if (tmp.slot >= 0) e->free_slots.push_back(tmp.slot);
+        set_last_error("ft_debug_prefill_logits: out of KV pages");
+        return -3;
+    }
     StepMeta& m = e->meta;
-    int* hh = m.h;
     int rc = 0;
     for (int p0 = 0; p0 < n && rc == 0; p0 += chunk) {
         const int len = std::min(chunk, n - p0);
         Batch b;
-        b.n_decode = 0; b.T = len; b.n_req = 1; b.n_prefill_req = 1; b.n_logit_rows = len;
+        fill_batch(e, {}, {Portion{&tmp, tokens + p0, len, p0}}, b);
+        for (int k = 0; k < len; ++k) m.h[m.o_lrow + k] = k;
+        b.n_logit_rows = len;
         b.logit_rows_identity = true;
-        layout_step(m, 1, e->max_pages, len);
-        for (int k = 0; k < len; ++k) {
-            hh[m.o_tokens + k] = tokens[p0 + k];
-            hh[m.o_pos + k] = p0 + k;
-            hh[m.o_rows + k] = 0;
-            hh[m.o_lrow + k] = k;
-        }
-        hh[m.o_qstart] = 0; hh[m.o_qstart + 1] = len;
-        hh[m.o_rslot] = 0; hh[m.o_rpos0] = p0;
-        for (size_t p = 0; p < tmp.pages.size(); ++p) hh[m.o_pt + p] = tmp.pages[p];
-        int tiles = 0;
-        for (int q0 = 0; q0 < len; q0 += 64, ++tiles) { hh[m.o_treq + tiles] = 0; hh[m.o_tq0 + tiles] = q0; }
-        b.n_tiles = tiles;
         rc = upload_meta(e);
         if (!rc) rc = forward(e, b);
         if (!rc && cudaMemcpyAsync(host_out + (size_t)p0 * e->cfg.vocab, e->logits, (size_t)len * e->cfg.vocab * 4,
@@ -1380,5 +1839,6 @@ extern "C" int ft_debug_prefill_logits(ft_engine* h, const int* tokens, int n, i
         }
     }
     release_pages_beyond(e, &tmp, 0);
+    if (tmp.slot >= 0) e->free_slots.push_back(tmp.slot);
     return rc;
 }

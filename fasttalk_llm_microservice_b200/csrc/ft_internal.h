@@ -2,6 +2,7 @@
 // include/fasttalk_b200.h.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -86,6 +87,64 @@ int launch_attn_prefill_tc(const void* q, int q_rows, const void* kv_layer, cons
                            const int* req_q_start, const int* req_slot, const int* req_pos0, const int* tile_req,
                            const int* tile_q0, int n_tiles, void* out, void* out_lo, int nq, int nkv, int d, bool pdl,
                            cudaStream_t stream);
+
+// ---- layered.cu (the layered model family: every size is a run-time value, activations fp32, weights bf16)
+enum { LIN_PLAIN = 0, LIN_SWIGLU_PAIR = 1, LIN_SOFTCAP = 2 };
+// C[r, n] = sum_k A[row(r), k] * W[p][n, k] for problems p = 0..P-1.
+//   batched (seg == null): every problem has rows 0..M-1; problem p reads A + p * a_col_stride, W + p * w_stride and
+//                          writes C + p * c_col_stride (heads side by side in the columns of one buffer)
+//   grouped (seg != null): problem p owns rows seg[p]..seg[p+1]-1 of C; row r reads A row a_rows[r] (or r)
+// LIN_SWIGLU_PAIR: W rows (2j, 2j+1) are (gate_j, up_j); C[r, j] = silu(gate) * up, ldc counts those N/2 columns.
+// LIN_SOFTCAP:     C = cap * tanh(C / cap).
+struct LinearArgs {
+    const float* A = nullptr;
+    const int* a_rows = nullptr;
+    const __nv_bfloat16* W = nullptr;
+    float* C = nullptr;
+    const int* seg = nullptr;
+    long long w_stride = 0;
+    int lda = 0, ldw = 0, ldc = 0, a_col_stride = 0, c_col_stride = 0;
+    int M = 0, N = 0, K = 0, P = 1, epi = LIN_PLAIN;
+    float cap = 0.f;
+};
+// rows_bound: M when batched; an upper bound of seg[P] when grouped
+int launch_linear(const LinearArgs& a, int rows_bound, cudaStream_t stream);
+int launch_embed_norm(const int* tokens, const void* embed, float* x, float* hn, int T, int W, float eps, float gain,
+                      cudaStream_t stream);
+int launch_combine_norm(float* x, float* hn, const float* proj, int ldp, int o_rg1, int o_rg2, const float* rg_bias,
+                        const float* mix, const float* eout, const float* wt, const int* slot_pos, int top, int T, int W,
+                        float eps, float gain, cudaStream_t stream);
+int launch_gather_rows(const float* src, const int* idx, float* dst, int n, int W, cudaStream_t stream);
+int launch_latent_write(const float* proj, int ldp, int o_dkv, const float* w, float* cache, const int* positions,
+                        const int* seq_rows, const int* page_table, int max_pages, int rank, float eps, int T,
+                        cudaStream_t stream);
+int launch_latent_attn(const float* qlat, const float* cache, const float* proj, int ldp, int o_gate, float* out,
+                       const int* positions, const int* seq_rows, const int* page_table, int max_pages, int H, int rank,
+                       float scale, int T, cudaStream_t stream);
+struct DeltaArgs {
+    const float* proj = nullptr;      // [T][ldp]: raw q | k | v at column o_q, beta logits at o_beta
+    int ldp = 0, o_q = 0, o_beta = 0;
+    const float* conv = nullptr;      // fp32 [channels][taps], last column = current token
+    const float* araw = nullptr;      // [T][heads*dim] decay pre-activation (before dt_bias)
+    const float* dt_bias = nullptr;   // [heads*dim]
+    const float* a_log = nullptr;     // [heads]
+    float* qkv = nullptr;             // out [T][channels]
+    float* decay = nullptr;           // out [T][heads*dim] (may alias araw)
+    float* beta = nullptr;            // out [T][heads]
+    float* o = nullptr;               // out [T][heads*vdim]
+    float* state = nullptr;           // slots of slot_stride floats; this layer's S at s_off, its tails at tail_off
+    long long slot_stride = 0, s_off = 0, tail_off = 0;
+    const int* seq_rows = nullptr;    // [T] request of a token
+    const int* req_start = nullptr;   // [n_req + 1] first row of a request
+    const int* req_pos0 = nullptr;    // [n_req] position of that row in its sequence
+    const int* req_slot = nullptr;    // [n_req] state slot
+    int heads = 0, kvh = 0, dim = 0, vdim = 0, taps = 0;
+};
+// prep (convolutions, norms, decays) -> tails -> recurrence -> output norm and gate (in place in a.o)
+int launch_delta(const DeltaArgs& a, const float* gate, const float* out_norm, float eps, int T, int n_req,
+                 cudaStream_t stream);
+int launch_route(const float* proj, int ldp, int o_router, int E, int top, int groups, int keep, int* ids, float* wts,
+                 int* seg, int* slot_token, int* slot_pos, int T, cudaStream_t stream);
 
 // ---- sampling.cu
 int launch_sample(const float* logits, int B, int V, const float* temperature, const int* top_k,

@@ -1,0 +1,714 @@
+// Kernels of the layered model family: decoders described layer by layer (ft_layer_desc), whose sizes are all run-time
+// values.  The residual stream, the normed layer input, every projection output, attention scores and weights, router
+// scores and the recurrent state are fp32; weights are bf16 and are multiplied as the fp32 numbers they are, with fp32
+// accumulation in a fixed order per output element — a row's result does not depend on which other rows share its launch.
+//
+//   linear              C[r, n] = sum_k A[row(r), k] * W[p][n, k]: plain, batched over heads (column offsets per problem)
+//                       or grouped over experts (row segments per problem, rows gathered through an index list), with
+//                       fused epilogues (paired SwiGLU, tanh soft cap); a 64 x 64 tile kernel for many rows and a
+//                       warp-per-output kernel for a handful of rows (decode)
+//   embed / combine     embedding gather; gated-residual update of the stream, both fused with the scalar-gain RMS norm
+//                       of the next layer
+//   latent attention    the latent of every token is normed and written to a paged fp32 cache; queries are folded into
+//                       latent space (q W_uk), scores, softmax and the weighted sum run over the cached latents, values
+//                       are expanded afterwards (W_uv): only the latent is ever stored
+//   channel delta       short causal convolutions + SiLU + unit norms + per-channel decays, then the gated delta rule
+//                       token by token with one thread per state column, state and convolution tails in per-session slots
+//   router              softmax over all experts, group-limited top-k, counting sort of (token, choice) pairs by expert
+#include "common.cuh"
+#include "ft_internal.h"
+
+namespace ft {
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_exact(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float bf16_to_f(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {      // red: >= 33 floats of shared memory
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// ------------------------------------------------------------------ linear: tile kernel
+constexpr int LBM = 64, LBN = 64, LBK = 16, LTHREADS = 256;
+
+template <bool VEC>
+__global__ void __launch_bounds__(LTHREADS) linear_tile_kernel(LinearArgs a) {
+    __shared__ float sA[LBK][LBM + 4];
+    __shared__ float sW[LBK][LBN + 4];
+    __shared__ int s_info[3];
+    int p, row0, rows_end;
+    if (a.seg) {                       // grouped: blockIdx.y enumerates the row tiles of all segments
+        if (threadIdx.x == 0) {
+            int tile = blockIdx.y, pp = 0, found = -1, r0 = 0, r1 = 0;
+            for (; pp < a.P; ++pp) {
+                const int s0 = a.seg[pp], s1 = a.seg[pp + 1];
+                const int nt = (s1 - s0 + LBM - 1) / LBM;
+                if (tile < nt) { found = pp; r0 = s0 + tile * LBM; r1 = s1; break; }
+                tile -= nt;
+            }
+            s_info[0] = found; s_info[1] = r0; s_info[2] = r1;
+        }
+        __syncthreads();
+        p = s_info[0]; row0 = s_info[1]; rows_end = s_info[2];
+        if (p < 0) return;
+    } else {
+        p = blockIdx.z; row0 = blockIdx.y * LBM; rows_end = a.M;
+    }
+    const int n0 = blockIdx.x * LBN;
+    const float* A = a.A + (size_t)p * a.a_col_stride;
+    const __nv_bfloat16* W = a.W + (size_t)p * a.w_stride;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;      // 16 x 16 threads, 4 x 4 outputs each
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    // loader mapping: thread -> (row within tile, 4 consecutive k)
+    const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 4;
+    const int arow_t = row0 + lr;
+    long long arow = -1;
+    if (arow_t < rows_end) arow = a.a_rows ? a.a_rows[arow_t] : arow_t;
+    const int wrow = n0 + lr;
+    for (int k0 = 0; k0 < a.K; k0 += LBK) {
+        float av[4] = {0.f, 0.f, 0.f, 0.f}, wv[4] = {0.f, 0.f, 0.f, 0.f};
+        const int k = k0 + lk;
+        if (arow >= 0) {
+            const float* ap = A + arow * a.lda + k;
+            if (VEC && k + 3 < a.K) {
+                const float4 t = *reinterpret_cast<const float4*>(ap);
+                av[0] = t.x; av[1] = t.y; av[2] = t.z; av[3] = t.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (k + i < a.K) av[i] = ap[i];
+            }
+        }
+        if (wrow < a.N) {
+            const __nv_bfloat16* wp = W + (size_t)wrow * a.ldw + k;
+            if (VEC && k + 3 < a.K) {
+                const uint2 t = *reinterpret_cast<const uint2*>(wp);
+                wv[0] = bf16_lo(t.x); wv[1] = bf16_hi(t.x); wv[2] = bf16_lo(t.y); wv[3] = bf16_hi(t.y);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (k + i < a.K) wv[i] = __bfloat162float(wp[i]);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { sA[lk + i][lr] = av[i]; sW[lk + i][lr] = wv[i]; }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < LBK; ++kk) {
+            const float4 x = *reinterpret_cast<const float4*>(&sA[kk][ty * 4]);
+            const float4 w = *reinterpret_cast<const float4*>(&sW[kk][tx * 4]);
+            const float xa[4] = {x.x, x.y, x.z, x.w}, wa[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xa[i], wa[j], acc[i][j]);
+        }
+    }
+    float* C = a.C + (size_t)p * a.c_col_stride;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = row0 + ty * 4 + i;
+        if (r >= rows_end) continue;
+        if (a.epi == LIN_SWIGLU_PAIR) {          // columns (2j, 2j+1) = (gate_j, up_j) -> C[r, j]
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int n = n0 + tx * 4 + j;
+                if (n + 1 < a.N) {
+                    const float g = acc[i][j];
+                    C[(size_t)r * a.ldc + (n >> 1)] = g / (1.f + expf(-g)) * acc[i][j + 1];
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = n0 + tx * 4 + j;
+                if (n < a.N) {
+                    float v = acc[i][j];
+                    if (a.epi == LIN_SOFTCAP) v = a.cap * tanhf(v / a.cap);
+                    C[(size_t)r * a.ldc + n] = v;
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ linear: few rows (decode)
+// One warp per output column (per pair of columns with the SwiGLU epilogue) and up to LROWS rows: the weights are read
+// once, 8 bytes per lane per load; the rows come from L1 / L2.
+constexpr int LROWS = 8;
+
+__global__ void __launch_bounds__(256) linear_rows_kernel(LinearArgs a) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const bool pair = a.epi == LIN_SWIGLU_PAIR;
+    const int cols = pair ? a.N / 2 : a.N;
+    const int p = blockIdx.y;
+    if (warp >= cols) return;
+    int r0 = 0, r1 = a.M;
+    if (a.seg) { r0 = a.seg[p]; r1 = a.seg[p + 1]; }
+    if (r1 <= r0) return;
+    const float* A = a.A + (size_t)p * a.a_col_stride;
+    const __nv_bfloat16* W = a.W + (size_t)p * a.w_stride;
+    float* C = a.C + (size_t)p * a.c_col_stride;
+    const int n = pair ? 2 * warp : warp;
+    const __nv_bfloat16* w0 = W + (size_t)n * a.ldw;
+    const __nv_bfloat16* w1 = w0 + a.ldw;
+    const bool vec = (a.K & 3) == 0 && (a.ldw & 3) == 0 && (a.lda & 3) == 0 && (a.a_col_stride & 3) == 0 &&
+                     ((a.w_stride & 3) == 0);
+    for (int rb = r0; rb < r1; rb += LROWS) {
+        const int nr = min(LROWS, r1 - rb);
+        const float* ar[LROWS];
+#pragma unroll
+        for (int i = 0; i < LROWS; ++i) {
+            const int r = rb + (i < nr ? i : 0);
+            ar[i] = A + (size_t)(a.a_rows ? a.a_rows[r] : r) * a.lda;
+        }
+        float acc0[LROWS], acc1[LROWS];
+#pragma unroll
+        for (int i = 0; i < LROWS; ++i) acc0[i] = acc1[i] = 0.f;
+        if (vec) {
+            for (int k = lane * 4; k < a.K; k += 128) {
+                const uint2 t = *reinterpret_cast<const uint2*>(w0 + k);
+                const float wa[4] = {bf16_lo(t.x), bf16_hi(t.x), bf16_lo(t.y), bf16_hi(t.y)};
+                float wb[4] = {0.f, 0.f, 0.f, 0.f};
+                if (pair) {
+                    const uint2 u = *reinterpret_cast<const uint2*>(w1 + k);
+                    wb[0] = bf16_lo(u.x); wb[1] = bf16_hi(u.x); wb[2] = bf16_lo(u.y); wb[3] = bf16_hi(u.y);
+                }
+#pragma unroll
+                for (int i = 0; i < LROWS; ++i) {
+                    if (i < nr) {
+                        const float4 x = *reinterpret_cast<const float4*>(ar[i] + k);
+                        acc0[i] = fmaf(x.x, wa[0], acc0[i]); acc0[i] = fmaf(x.y, wa[1], acc0[i]);
+                        acc0[i] = fmaf(x.z, wa[2], acc0[i]); acc0[i] = fmaf(x.w, wa[3], acc0[i]);
+                        if (pair) {
+                            acc1[i] = fmaf(x.x, wb[0], acc1[i]); acc1[i] = fmaf(x.y, wb[1], acc1[i]);
+                            acc1[i] = fmaf(x.z, wb[2], acc1[i]); acc1[i] = fmaf(x.w, wb[3], acc1[i]);
+                        }
+                    }
+                }
+            }
+        } else {
+            for (int k = lane; k < a.K; k += 32) {
+                const float wa = __bfloat162float(w0[k]);
+                const float wb = pair ? __bfloat162float(w1[k]) : 0.f;
+#pragma unroll
+                for (int i = 0; i < LROWS; ++i)
+                    if (i < nr) {
+                        const float x = ar[i][k];
+                        acc0[i] = fmaf(x, wa, acc0[i]);
+                        acc1[i] = fmaf(x, wb, acc1[i]);
+                    }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < LROWS; ++i) {
+            if (i >= nr) continue;               // uniform over the warp
+            const float s0 = warp_sum(acc0[i]);
+            const float s1 = pair ? warp_sum(acc1[i]) : 0.f;
+            if (lane == 0) {
+                float v = s0;
+                if (pair) v = s0 / (1.f + expf(-s0)) * s1;
+                else if (a.epi == LIN_SOFTCAP) v = a.cap * tanhf(v / a.cap);
+                C[(size_t)(rb + i) * a.ldc + warp] = v;
+            }
+        }
+    }
+}
+
+int launch_linear(const LinearArgs& a, int rows_bound, cudaStream_t stream) {
+    if (rows_bound <= 0 || a.N <= 0) return 0;
+    FT_REQUIRE(a.K >= 1 && a.P >= 1, "linear: bad sizes");
+    FT_REQUIRE(a.epi != LIN_SWIGLU_PAIR || (a.N & 1) == 0, "linear: the paired epilogue needs an even number of rows");
+    // few rows per problem: one warp per output column, the weights stream once
+    const bool few = a.seg ? rows_bound <= 2 * LROWS : rows_bound <= LROWS;
+    if (few) {
+        const int cols = a.epi == LIN_SWIGLU_PAIR ? a.N / 2 : a.N;
+        dim3 grid((cols + 7) / 8, a.P);
+        linear_rows_kernel<<<grid, 256, 0, stream>>>(a);
+        FT_CHECK_CUDA(cudaGetLastError());
+        return 0;
+    }
+    const bool vec = (a.lda & 3) == 0 && (a.ldw & 3) == 0 && (a.a_col_stride & 3) == 0 && (a.w_stride & 3) == 0 &&
+                     ((uintptr_t)a.A & 15) == 0 && ((uintptr_t)a.W & 7) == 0;
+    dim3 grid((a.N + LBN - 1) / LBN, 1, 1);
+    if (a.seg) grid.y = (rows_bound + LBM - 1) / LBM + a.P;
+    else { grid.y = (a.M + LBM - 1) / LBM; grid.z = a.P; }
+    if (vec) linear_tile_kernel<true><<<grid, LTHREADS, 0, stream>>>(a);
+    else linear_tile_kernel<false><<<grid, LTHREADS, 0, stream>>>(a);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------ embedding / residual update, fused with the next norm
+// hn[t] = x[t] / sqrt(mean(x[t]^2) + eps) * gain, the gain being one number.
+__global__ void __launch_bounds__(256)
+embed_norm_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ embed, float* __restrict__ x,
+                  float* __restrict__ hn, int W, float eps, float gain) {
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    const __nv_bfloat16* e = embed + (size_t)tokens[t] * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = __bfloat162float(e[c]);
+        x[(size_t)t * W + c] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float r = gain / sqrtf(ss / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) hn[(size_t)t * W + c] = __bfloat162float(e[c]) * r;
+}
+
+// x[t] += sigmoid(rg1[t] + b1) * mix[t] + sigmoid(rg2[t] + b2) * sum_k wt[t, k] * eout[slot_pos[t, k]]   (feed-forward
+// part only when top > 0), then the next norm of the row.  rg1 / rg2 are column ranges of the input projection `proj`.
+__global__ void __launch_bounds__(256)
+combine_norm_kernel(float* __restrict__ x, float* __restrict__ hn, const float* __restrict__ proj, int ldp, int o_rg1,
+                    int o_rg2, const float* __restrict__ rg_bias, const float* __restrict__ mix,
+                    const float* __restrict__ eout, const float* __restrict__ wt, const int* __restrict__ slot_pos,
+                    int top, int W, float eps, float gain) {
+    __shared__ float red[33];
+    extern __shared__ float row[];
+    const int t = blockIdx.x;
+    const float* pr = proj + (size_t)t * ldp;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float y = sigmoid_exact(pr[o_rg1 + c] + rg_bias[c]) * mix[(size_t)t * W + c];
+        if (top > 0) {
+            float f = 0.f;
+            for (int k = 0; k < top; ++k)
+                f = fmaf(wt[(size_t)t * top + k], eout[(size_t)slot_pos[(size_t)t * top + k] * W + c], f);
+            y += sigmoid_exact(pr[o_rg2 + c] + rg_bias[W + c]) * f;
+        }
+        const float v = x[(size_t)t * W + c] + y;
+        x[(size_t)t * W + c] = v;
+        row[c] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float r = gain / sqrtf(ss / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) hn[(size_t)t * W + c] = row[c] * r;
+}
+
+// rows of the normed stream that the head reads: out[i] = hn[idx[i]]
+__global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ idx, float* __restrict__ dst, int W) {
+    const int i = blockIdx.x;
+    const float* s = src + (size_t)idx[i] * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) dst[(size_t)i * W + c] = s[c];
+}
+
+int launch_embed_norm(const int* tokens, const void* embed, float* x, float* hn, int T, int W, float eps, float gain,
+                      cudaStream_t stream) {
+    embed_norm_kernel<<<T, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)embed, x, hn, W, eps, gain);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+int launch_combine_norm(float* x, float* hn, const float* proj, int ldp, int o_rg1, int o_rg2, const float* rg_bias,
+                        const float* mix, const float* eout, const float* wt, const int* slot_pos, int top, int T, int W,
+                        float eps, float gain, cudaStream_t stream) {
+    combine_norm_kernel<<<T, 256, (size_t)W * 4, stream>>>(x, hn, proj, ldp, o_rg1, o_rg2, rg_bias, mix, eout, wt, slot_pos,
+                                                          top, W, eps, gain);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+int launch_gather_rows(const float* src, const int* idx, float* dst, int n, int W, cudaStream_t stream) {
+    gather_rows_kernel<<<n, 256, 0, stream>>>(src, idx, dst, W);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------ latent attention
+// The latent of token t: c = raw / sqrt(mean(raw^2) + eps) * w, written to page_table[seq_rows[t]][pos / 64], row pos % 64
+// of the layer's cache [page][64][rank] fp32.
+__global__ void __launch_bounds__(128)
+latent_write_kernel(const float* __restrict__ proj, int ldp, int o_dkv, const float* __restrict__ w, float* __restrict__ cache,
+                    const int* __restrict__ positions, const int* __restrict__ seq_rows, const int* __restrict__ page_table,
+                    int max_pages, int rank, float eps) {
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    const float* raw = proj + (size_t)t * ldp + o_dkv;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) ss += raw[c] * raw[c];
+    ss = block_sum(ss, red);
+    const float r = 1.f / sqrtf(ss / (float)rank + eps);
+    const int pos = positions[t];
+    const int page = page_table[(size_t)seq_rows[t] * max_pages + pos / kKvTile];
+    float* dst = cache + ((size_t)page * kKvTile + pos % kKvTile) * rank;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) dst[c] = raw[c] * r * w[c];
+}
+
+// One warp per (token, head): the query in latent space stays in registers (NR values per lane), keys = values = the
+// cached latents of positions 0..pos, online softmax in fp32.  The head's result is scaled by its output gate
+// sigmoid(gate logit): the value expansion that follows is linear, so gating before it is the same.
+template <int NR>
+__global__ void __launch_bounds__(128)
+latent_attn_kernel(const float* __restrict__ qlat, const float* __restrict__ cache, const float* __restrict__ proj, int ldp,
+                   int o_gate, float* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_rows,
+                   const int* __restrict__ page_table, int max_pages, int H, int rank, float scale, int n_pairs) {
+    const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (pair >= n_pairs) return;
+    const int t = pair / H, h = pair % H;
+    const float* q = qlat + ((size_t)t * H + h) * rank;
+    float qr[NR], acc[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        const int c = lane + 32 * i;
+        qr[i] = c < rank ? q[c] * scale : 0.f;
+        acc[i] = 0.f;
+    }
+    const int pos = positions[t];
+    const int* pt = page_table + (size_t)seq_rows[t] * max_pages;
+    float m = -INFINITY, l = 0.f;
+    for (int j0 = 0; j0 <= pos; j0 += kKvTile) {
+        const float* pg = cache + (size_t)pt[j0 / kKvTile] * kKvTile * rank;
+        const int nj = min(kKvTile, pos + 1 - j0);
+        for (int j = 0; j < nj; ++j) {
+            const float* c = pg + (size_t)j * rank;
+            float cv[NR], s = 0.f;
+#pragma unroll
+            for (int i = 0; i < NR; ++i) {
+                const int cc = lane + 32 * i;
+                cv[i] = cc < rank ? c[cc] : 0.f;
+                s = fmaf(qr[i], cv[i], s);
+            }
+            s = warp_sum(s);
+            const float mn = fmaxf(m, s);
+            const float corr = expf(m - mn), pw = expf(s - mn);
+            l = l * corr + pw;
+#pragma unroll
+            for (int i = 0; i < NR; ++i) acc[i] = fmaf(pw, cv[i], acc[i] * corr);
+            m = mn;
+        }
+    }
+    const float g = sigmoid_exact(proj[(size_t)t * ldp + o_gate + h]) / l;
+    float* o = out + ((size_t)t * H + h) * rank;
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        const int c = lane + 32 * i;
+        if (c < rank) o[c] = acc[i] * g;
+    }
+}
+
+int launch_latent_write(const float* proj, int ldp, int o_dkv, const float* w, float* cache, const int* positions,
+                        const int* seq_rows, const int* page_table, int max_pages, int rank, float eps, int T,
+                        cudaStream_t stream) {
+    latent_write_kernel<<<T, 128, 0, stream>>>(proj, ldp, o_dkv, w, cache, positions, seq_rows, page_table, max_pages, rank, eps);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_latent_attn(const float* qlat, const float* cache, const float* proj, int ldp, int o_gate, float* out,
+                       const int* positions, const int* seq_rows, const int* page_table, int max_pages, int H, int rank,
+                       float scale, int T, cudaStream_t stream) {
+    const int n_pairs = T * H;
+    const dim3 grid((n_pairs + 3) / 4);
+#define FT_LAT(NR_)                                                                                                      \
+    latent_attn_kernel<NR_><<<grid, 128, 0, stream>>>(qlat, cache, proj, ldp, o_gate, out, positions, seq_rows, page_table, \
+                                                      max_pages, H, rank, scale, n_pairs)
+    if (rank <= 32) FT_LAT(1);
+    else if (rank <= 64) FT_LAT(2);
+    else if (rank <= 128) FT_LAT(4);
+    else if (rank <= 256) FT_LAT(8);
+    else if (rank <= 512) FT_LAT(16);
+    else { FT_REQUIRE(rank <= 1024, "latent attention: latent size %d is beyond 1024", rank); FT_LAT(32); }
+#undef FT_LAT
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------ channel delta
+// Per token: the three short convolutions over time + SiLU (inputs before the step's first token come from the session's
+// tail of raw inputs; zeros before position 0), unit norms of q and k per head (q also times dim^-1/2), the decay
+// exp(-exp(A_log_h) * softplus(a + dt_bias)) per head and key channel, beta = sigmoid.
+// qkv out: [T][channels] with channels = 2 * kvh * dim + heads * vdim in the order q | k | v.
+__global__ void __launch_bounds__(256)
+delta_prep_kernel(DeltaArgs a) {
+    extern __shared__ float sh[];
+    const int t = blockIdx.x;
+    const int req = a.seq_rows[t];
+    const int r = t - a.req_start[req];              // index inside this step's portion
+    const int pos0 = a.req_pos0[req];
+    const int qk = a.kvh * a.dim, ch = 2 * qk + a.heads * a.vdim;
+    const float* tail = a.state + (size_t)a.req_slot[req] * a.slot_stride + a.tail_off;
+    const int taps = a.taps;
+    for (int c = threadIdx.x; c < ch; c += blockDim.x) {
+        float s = 0.f;
+        for (int i = 0; i < taps; ++i) {
+            const int back = taps - 1 - i;
+            float v;
+            if (r - back >= 0) v = a.proj[(size_t)(t - back) * a.ldp + a.o_q + c];
+            else if (pos0 + r - back >= 0) v = tail[(size_t)c * (taps - 1) + (taps - 1 + r - back)];
+            else v = 0.f;
+            s = fmaf(a.conv[(size_t)c * taps + i], v, s);
+        }
+        sh[c] = s / (1.f + expf(-s));
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float* dst = a.qkv + (size_t)t * ch;
+    for (int hh = wid; hh < 2 * a.kvh; hh += nw) {          // q heads, then k heads
+        const float* v = sh + (size_t)hh * a.dim;
+        float ss = 0.f;
+        for (int d = lane; d < a.dim; d += 32) ss += v[d] * v[d];
+        ss = warp_sum(ss);
+        float sc = 1.f / sqrtf(ss + 1e-6f);
+        if (hh < a.kvh) sc *= 1.f / sqrtf((float)a.dim);
+        for (int d = lane; d < a.dim; d += 32) dst[(size_t)hh * a.dim + d] = v[d] * sc;
+    }
+    for (int c = 2 * qk + threadIdx.x; c < ch; c += blockDim.x) dst[c] = sh[c];
+    const int hd = a.heads * a.dim;
+    for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+        const float z = a.araw[(size_t)t * hd + i] + a.dt_bias[i];
+        const float sp = z > 20.f ? z : log1pf(expf(z));
+        a.decay[(size_t)t * hd + i] = expf(-expf(a.a_log[i / a.dim]) * sp);
+    }
+    for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
+        a.beta[(size_t)t * a.heads + h] = sigmoid_exact(a.proj[(size_t)t * a.ldp + a.o_beta + h]);
+}
+
+// New tail of raw convolution inputs per (request, channel): the last taps-1 entries of (old tail ++ this step's inputs).
+__global__ void delta_tail_kernel(DeltaArgs a, int n_req) {
+    const int req = blockIdx.y;
+    const int ch = 2 * a.kvh * a.dim + a.heads * a.vdim;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= ch || req >= n_req) return;
+    const int n = a.req_start[req + 1] - a.req_start[req], pos0 = a.req_pos0[req], keep = a.taps - 1;
+    float* tail = a.state + (size_t)a.req_slot[req] * a.slot_stride + a.tail_off + (size_t)c * keep;
+    float v[16];
+    for (int i = 0; i < keep; ++i) {
+        const int src = n + i;                      // index into old tail (keep entries) ++ inputs (n entries)
+        if (src < keep) v[i] = pos0 > 0 ? tail[src] : 0.f;
+        else v[i] = a.proj[(size_t)(a.req_start[req] + src - keep) * a.ldp + a.o_q + c];
+    }
+    for (int i = 0; i < keep; ++i) tail[i] = v[i];
+}
+
+// The recurrence, one CTA per (request, head), one thread per column of the state S [dim][vdim]: per token
+//   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+// is local to a column, so no thread talks to another; q, k, g, v of a few tokens are staged in shared memory at a time.
+constexpr int DCHUNK = 8;
+template <int DMAX>
+__global__ void __launch_bounds__(256)
+delta_rule_kernel(DeltaArgs a) {
+    extern __shared__ float sh[];
+    const int req = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+    const int kh = h / (a.heads / a.kvh);
+    const int row0 = a.req_start[req], n = a.req_start[req + 1] - row0;
+    const int dim = a.dim, vdim = a.vdim;
+    const int qk = a.kvh * dim, ch = 2 * qk + a.heads * vdim;
+    float* S = a.state + (size_t)a.req_slot[req] * a.slot_stride + a.s_off + (size_t)h * dim * vdim;
+    float s[DMAX];
+    const bool live = j < vdim;
+    const bool fresh = a.req_pos0[req] == 0;
+#pragma unroll
+    for (int d = 0; d < DMAX; ++d) s[d] = (live && !fresh && d < dim) ? S[(size_t)d * vdim + j] : 0.f;
+    // shared: per staged token  q[dim] k[dim] g[dim] v[vdim] beta
+    const int per = 3 * dim + vdim + 1;
+    for (int c0 = 0; c0 < n; c0 += DCHUNK) {
+        const int nc = min(DCHUNK, n - c0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nc * per; i += blockDim.x) {
+            const int tt = i / per, e = i % per;
+            const size_t t = row0 + c0 + tt;
+            float v;
+            if (e < dim) v = a.qkv[t * ch + (size_t)kh * dim + e];
+            else if (e < 2 * dim) v = a.qkv[t * ch + qk + (size_t)kh * dim + (e - dim)];
+            else if (e < 3 * dim) v = a.decay[t * ((size_t)a.heads * dim) + (size_t)h * dim + (e - 2 * dim)];
+            else if (e < 3 * dim + vdim) v = a.qkv[t * ch + 2 * qk + (size_t)h * vdim + (e - 3 * dim)];
+            else v = a.beta[t * a.heads + h];
+            sh[i] = v;
+        }
+        __syncthreads();
+        if (live) {
+            for (int tt = 0; tt < nc; ++tt) {
+                const float* q = sh + (size_t)tt * per;
+                const float* k = q + dim;
+                const float* g = k + dim;
+                float dot = 0.f;
+#pragma unroll
+                for (int d = 0; d < DMAX; ++d)
+                    if (d < dim) { s[d] *= g[d]; dot = fmaf(s[d], k[d], dot); }
+                const float u = g[dim + vdim] * (g[dim + j] - dot);
+                float o = 0.f;
+#pragma unroll
+                for (int d = 0; d < DMAX; ++d)
+                    if (d < dim) { s[d] = fmaf(k[d], u, s[d]); o = fmaf(s[d], q[d], o); }
+                a.o[(size_t)(row0 + c0 + tt) * ((size_t)a.heads * vdim) + (size_t)h * vdim + j] = o;
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int d = 0; d < DMAX; ++d)
+            if (d < dim) S[(size_t)d * vdim + j] = s[d];
+    }
+}
+
+// o[t, h, :] <- o / sqrt(mean(o^2) + eps) * w * sigmoid(gate[t, h, :]), one warp per (token, head)
+__global__ void __launch_bounds__(128)
+delta_out_kernel(float* __restrict__ o, const float* __restrict__ gate, const float* __restrict__ w, int vdim, float eps,
+                 int n_pairs) {
+    const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (pair >= n_pairs) return;
+    float* p = o + (size_t)pair * vdim;
+    const float* g = gate + (size_t)pair * vdim;
+    float ss = 0.f;
+    for (int c = lane; c < vdim; c += 32) ss += p[c] * p[c];
+    ss = warp_sum(ss);
+    const float r = 1.f / sqrtf(ss / (float)vdim + eps);
+    for (int c = lane; c < vdim; c += 32) p[c] = p[c] * r * w[c] * sigmoid_exact(g[c]);
+}
+
+int launch_delta(const DeltaArgs& a, const float* gate, const float* out_norm, float eps, int T, int n_req,
+                 cudaStream_t stream) {
+    const int ch = 2 * a.kvh * a.dim + a.heads * a.vdim;
+    FT_REQUIRE(a.taps >= 1 && a.taps <= 17, "channel delta: %d convolution taps are beyond 17", a.taps);
+    FT_REQUIRE(a.dim <= 256 && a.vdim <= 256, "channel delta: head sizes %d / %d are beyond 256", a.dim, a.vdim);
+    FT_REQUIRE((size_t)ch * 4 <= 200 * 1024, "channel delta: %d channels do not fit in shared memory", ch);
+    static PerDeviceFlag attr;
+    if (!attr.done()) {
+        FT_CHECK_CUDA(cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr.mark();
+    }
+    delta_prep_kernel<<<T, 256, (size_t)ch * 4, stream>>>(a);
+    FT_CHECK_CUDA(cudaGetLastError());
+    if (a.taps > 1) {
+        delta_tail_kernel<<<dim3((ch + 127) / 128, n_req), 128, 0, stream>>>(a, n_req);
+        FT_CHECK_CUDA(cudaGetLastError());
+    }
+    const int threads = (a.vdim + 31) / 32 * 32;
+    const size_t smem = (size_t)DCHUNK * (3 * a.dim + a.vdim + 1) * 4;
+    const dim3 grid(n_req, a.heads);
+    if (a.dim <= 32) delta_rule_kernel<32><<<grid, threads, smem, stream>>>(a);
+    else if (a.dim <= 64) delta_rule_kernel<64><<<grid, threads, smem, stream>>>(a);
+    else if (a.dim <= 128) delta_rule_kernel<128><<<grid, threads, smem, stream>>>(a);
+    else delta_rule_kernel<256><<<grid, threads, smem, stream>>>(a);
+    FT_CHECK_CUDA(cudaGetLastError());
+    const int n_pairs = T * a.heads;
+    delta_out_kernel<<<(n_pairs + 3) / 4, 128, 0, stream>>>(a.o, gate, out_norm, a.vdim, eps, n_pairs);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------ router
+// One warp per token: s = softmax(z) over all E experts; a group's score is its largest s; only experts of the `keep`
+// best groups can be chosen; the `top` largest s among them, lowest index first on a tie; weights = s as it is.
+__global__ void __launch_bounds__(128)
+route_kernel(const float* __restrict__ proj, int ldp, int o_router, int E, int top, int groups, int keep, int* __restrict__ ids,
+             float* __restrict__ wts, int T) {
+    extern __shared__ float sh[];
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + wid;
+    if (t >= T) return;
+    float* s = sh + (size_t)wid * (E + groups);     // scores, then group scores; a taken entry is set to -1
+    float* gs = s + E;
+    const float* z = proj + (size_t)t * ldp + o_router;
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float v = expf(z[e] - m); s[e] = v; sum += v; }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
+    __syncwarp();
+    const int per = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+        float b = -1.f;
+        for (int i = 0; i < per; ++i) b = fmaxf(b, s[g * per + i]);
+        gs[g] = b;
+    }
+    __syncwarp();
+    // drop the groups that are not among the best `keep`: groups - keep rounds of "remove the smallest" would favour the
+    // wrong side of ties, so pick the best `keep` and mark them by negating (score + 2)
+    for (int r = 0; r < keep; ++r) {
+        float bv = -1.f; int bi = 0x7fffffff;
+        for (int g = lane; g < groups; g += 32) if (gs[g] >= 0.f && (gs[g] > bv)) { bv = gs[g]; bi = g; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0 && bi < groups) gs[bi] = -(bv + 2.f);
+        __syncwarp();
+    }
+    for (int r = 0; r < top; ++r) {
+        float bv = -1.f; int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] < -1.f && s[e] >= 0.f && s[e] > bv) { bv = s[e]; bi = e; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            const int e = bi < E ? bi : 0;
+            ids[(size_t)t * top + r] = e;
+            wts[(size_t)t * top + r] = bi < E ? bv : 0.f;
+            if (bi < E) s[bi] = -1.f;
+        }
+        __syncwarp();
+    }
+}
+
+// Counting sort of the T * top (token, choice) pairs by expert, one CTA: seg[e] .. seg[e+1] are the sorted places of
+// expert e, slot_token[place] the token whose row the expert reads, slot_pos[pair] the place of a pair.  Within an expert the
+// order is (token, choice) order, so the layout is the same from run to run.
+__global__ void __launch_bounds__(1024)
+route_sort_kernel(const int* __restrict__ ids, int n_pairs, int top, int E, int* __restrict__ seg, int* __restrict__ slot_token,
+                  int* __restrict__ slot_pos) {
+    extern __shared__ int shi[];
+    int* cnt = shi;                    // [E + 1]
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&cnt[ids[i] + 1], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int e = 0; e < E; ++e) cnt[e + 1] += cnt[e];
+        for (int e = 0; e <= E; ++e) seg[e] = cnt[e];
+    }
+    __syncthreads();
+    // stable placement: a warp per expert walks the pairs in order (ballot + prefix count)
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int e = wid; e < E; e += nw) {
+        int base = cnt[e];
+        for (int i0 = 0; i0 < n_pairs; i0 += 32) {
+            const int i = i0 + lane;
+            const bool mine = i < n_pairs && ids[i] == e;
+            const unsigned b = __ballot_sync(0xffffffffu, mine);
+            if (mine) {
+                const int place = base + __popc(b & ((1u << lane) - 1u));
+                slot_token[place] = i / top;
+                slot_pos[i] = place;
+            }
+            base += __popc(b);
+        }
+    }
+}
+
+int launch_route(const float* proj, int ldp, int o_router, int E, int top, int groups, int keep, int* ids, float* wts,
+                 int* seg, int* slot_token, int* slot_pos, int T, cudaStream_t stream) {
+    FT_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups && top >= 1 && top <= (E / groups) * keep,
+               "router: %d experts, %d groups, keep %d, top %d do not fit together", E, groups, keep, top);
+    const size_t smem = (size_t)4 * (E + groups) * 4;
+    FT_REQUIRE(smem <= 48 * 1024 && (size_t)(E + 1) * 4 <= 48 * 1024, "router: %d experts are too many", E);
+    route_kernel<<<(T + 3) / 4, 128, smem, stream>>>(proj, ldp, o_router, E, top, groups, keep, ids, wts, T);
+    FT_CHECK_CUDA(cudaGetLastError());
+    route_sort_kernel<<<1, 1024, (size_t)(E + 1) * 4, stream>>>(ids, T * top, top, E, seg, slot_token, slot_pos);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace ft

@@ -15,6 +15,7 @@ import numpy as np
 import torch
 
 from . import native as N
+from .layered import LayeredSpec, pack as pack_layered
 from .model_spec import ModelSpec
 from .weights import interleave_gate_up, rope_tables
 
@@ -56,6 +57,9 @@ class Engine:
         self.limits = lim = limits or EngineLimits()
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         torch.cuda.set_device(self.device)
+        if isinstance(spec, LayeredSpec):
+            self._init_layered(spec, weights, lim, eos_ids)
+            return
         if tp_size > 1:
             from .tp import shard_spec, shard_weights
             weights = shard_weights(spec, weights, tp_rank, tp_size)
@@ -100,6 +104,34 @@ class Engine:
         self._h = self.lib.ft_engine_create(C.byref(cfg), C.byref(wt))
         if not self._h:
             raise N.NativeError(f"ft_engine_create failed: {N.last_error()}")
+        self._drain_buffers(lim)
+
+    def _init_layered(self, spec: LayeredSpec, weights, lim: EngineLimits, eos_ids):
+        """A layered model (layered.py): tensors by their checkpoint names -> the engine's arrays and descriptors."""
+        if self.tp_size > 1:
+            raise N.NativeError("tensor parallelism is built for the Llama models only")
+        self.spec = spec
+        model, self._keep = pack_layered(spec, weights, self.device)
+        pages_per_ctx = -(-lim.max_context // 64)
+        num_pages = lim.num_pages or int(lim.max_batch * pages_per_ctx * 1.25) + 8
+        cfg = N.EngineConfig()
+        cfg.hidden, cfg.layers, cfg.vocab, cfg.rms_eps = spec.width, len(spec.layers), spec.vocab, spec.eps
+        cfg.max_batch, cfg.max_batched_tokens = lim.max_batch, max(lim.max_batched_tokens, lim.max_batch)
+        cfg.num_pages, cfg.max_context = num_pages, lim.max_context
+        cfg.max_sessions = lim.max_sessions or 4 * lim.max_batch
+        eos = [e for e in eos_ids if 0 <= e < spec.vocab][:4]
+        cfg.n_eos = len(eos)
+        for i, e in enumerate(eos):
+            cfg.eos_ids[i] = e
+        cfg.debug_logit_rows = lim.debug_logit_rows
+        cfg.decode_prefill_cap = lim.decode_prefill_cap
+        self.num_pages = num_pages
+        self._h = self.lib.ft_engine_create_layered(C.byref(cfg), C.addressof(model))
+        if not self._h:
+            raise N.NativeError(f"ft_engine_create_layered failed: {N.last_error()}")
+        self._drain_buffers(lim)
+
+    def _drain_buffers(self, lim: EngineLimits):
         cap = 4 * lim.max_batch + 64
         self._cap = cap
         self._d_req = np.empty(cap, dtype=np.int64)
@@ -203,6 +235,32 @@ class Engine:
         out = np.empty(self.spec.vocab, dtype=np.float32)
         N.check(self.lib.ft_engine_get_logits(self._h, rid, out.ctypes.data), "ft_engine_get_logits")
         return torch.from_numpy(out)
+
+    def feed(self, entries: Sequence[Tuple[object, Sequence[int], Sequence[int]]]) -> np.ndarray:
+        """One step over given tokens (ft_engine_feed): entries of (session, its next tokens, the places among them whose
+        logits are wanted).  All entries run as one batch; returns float32 [wanted, vocab] in entry order."""
+        keys = np.array([session_key(s) for s, _, _ in entries], dtype=np.uint64)
+        counts = np.array([len(t) for _, t, _ in entries], dtype=np.int32)
+        toks = np.ascontiguousarray(np.concatenate([np.asarray(t, dtype=np.int32) for _, t, _ in entries]))
+        want, off = [], 0
+        for _, t, wn in entries:
+            want += [off + int(i) for i in wn]
+            off += len(t)
+        want = np.array(want, dtype=np.int32)
+        out = np.empty((len(want), self.spec.vocab), dtype=np.float32)
+        N.check(self.lib.ft_engine_feed(self._h, len(entries), keys.ctypes.data, counts.ctypes.data, toks.ctypes.data,
+                                        len(want), want.ctypes.data if len(want) else None,
+                                        out.ctypes.data if len(want) else None), "ft_engine_feed")
+        return out
+
+    def debug_trail(self, on: bool = True):
+        N.check(self.lib.ft_engine_debug_trail(self._h, int(on)), "ft_engine_debug_trail")
+
+    def read_trail(self, rows: int) -> np.ndarray:
+        """Residual stream after every layer of the most recent step: float32 [layers, rows, width]."""
+        out = np.empty((len(self.spec.layers), rows, self.spec.width), dtype=np.float32)
+        N.check(self.lib.ft_engine_debug_read_trail(self._h, out.ctypes.data, rows), "ft_engine_debug_read_trail")
+        return out
 
     def debug_prefill_logits(self, tokens: Sequence[int], chunk: int = 64) -> torch.Tensor:
         arr = np.ascontiguousarray(tokens, dtype=np.int32)

@@ -77,6 +77,10 @@ _VP, _I, _LL, _F, _ULL = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulong
 SIGNATURES = {
     "ft_last_error": (C.c_char_p, []),
     "ft_engine_create": (_VP, [C.POINTER(EngineConfig), C.POINTER(Weights)]),
+    "ft_engine_create_layered": (_VP, [C.POINTER(EngineConfig), _VP]),
+    "ft_engine_feed": (_I, [_VP, _I, _VP, _VP, _VP, _I, _VP, _VP]),
+    "ft_engine_debug_trail": (_I, [_VP, _I]),
+    "ft_engine_debug_read_trail": (_I, [_VP, _VP, _I]),
     "ft_engine_destroy": (None, [_VP]),
     "ft_engine_submit": (_LL, [_VP, _ULL, _VP, _I, _F, _I, _F, _I, _ULL, _I]),
     "ft_engine_step": (_I, [_VP]),

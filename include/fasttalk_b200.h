@@ -173,6 +173,80 @@ int ft_engine_get_logits(ft_engine* e, long long req, float* host_out);
 int ft_debug_prefill_logits(ft_engine* e, const int* tokens, int n_tokens, int chunk, float* host_out);
 
 /* ------------------------------------------------------------------------------------------
+ * Layered models — decoders described layer by layer instead of by the Llama field set above: each layer names
+ * its token mixer (latent attention over a paged latent cache, or a gated delta rule with per-channel decay whose
+ * state lives in a per-session slot) and its feed-forward (none, or a mixture of experts with group-limited
+ * routing).  Every size is a run-time value.  The engine around them is the same one: page allocator, session
+ * table, continuous-batching scheduler, sampling, stepping thread.  No counterpart in the reference, which names
+ * models by tag and owns no model code (app/utils/config.py:86).
+ *
+ * A layer:  h = x / sqrt(mean(x^2) + eps) * norm_gain;  x += sigmoid(W_rg1 h + b1) * mixer(h) + sigmoid(W_rg2 h + b2) * ff(h)
+ * (both sublayers read the same h).  All projections that read h are stacked into ONE matrix w_in whose output
+ * columns are addressed by the o_* offsets (-1 = the layer has no such part).
+ * Small vectors are fp32 device arrays; matrices are bf16 [out, in] row-major.
+ * ---------------------------------------------------------------------------------------- */
+enum { FT_MIXER_LATENT_ATTENTION = 1, FT_MIXER_CHANNEL_DELTA = 2 };
+enum { FT_FF_NONE = 0, FT_FF_MOE = 1 };
+typedef struct {
+    int mixer;                 /* FT_MIXER_* */
+    int heads, kv_heads;       /* channel delta: q / k have kv_heads heads, head h reads q/k head h / (heads / kv_heads) */
+    int dim, vdim;             /* per head: query/key size, value size */
+    int kv_rank;               /* latent attention: size of the cached latent */
+    float scale;               /* latent attention: score = (q . k) * scale */
+    int conv;                  /* channel delta: taps of the short causal convolutions on q, k, v */
+    int rank_a, rank_g;        /* channel delta: inner sizes of the low-rank decay and gate projections */
+    int ff_kind;               /* FT_FF_* */
+    int experts, top, groups, keep, ff;
+    int n_in;                  /* rows of w_in */
+    int o_q, o_k, o_v, o_dkv, o_gate, o_beta, o_a1, o_g1, o_rg1, o_rg2, o_router;
+    float norm_gain;           /* the layer norm's single gain */
+    const void* w_in;          /* bf16 [n_in, width] */
+    const void* w_o;           /* bf16 [width, heads * vdim] */
+    const float* rg_bias;      /* fp32 [2 * width]: b1 | b2 */
+    /* latent attention: keys k_h = W_uk_h c and values v_h = W_uv_h c are never formed; the query is folded instead */
+    const void* w_uk_t;        /* bf16 [heads][kv_rank][dim]: W_uk of each head, transposed */
+    const void* w_uv;          /* bf16 [heads * vdim, kv_rank] */
+    const float* dkv_norm;     /* fp32 [kv_rank] */
+    /* channel delta */
+    const float* conv_w;       /* fp32 [2 * kv_heads * dim + heads * vdim][conv], rows in the order q | k | v */
+    const void* w_a2;          /* bf16 [heads * dim, rank_a] */
+    const void* w_g2;          /* bf16 [heads * vdim, rank_g] */
+    const float* dt_bias;      /* fp32 [heads * dim] */
+    const float* a_log;        /* fp32 [heads] */
+    const float* out_norm;     /* fp32 [vdim] */
+    /* mixture of experts */
+    const void* w_gu;          /* bf16 [experts][2 * ff][width], rows (2j, 2j+1) = (gate_j, up_j) */
+    const void* w_down;        /* bf16 [experts][width][ff] */
+} ft_layer_desc;
+
+typedef struct {
+    int width, vocab, n_layers;
+    float eps;                 /* of every RMS norm of the model */
+    float logit_softcap;       /* logits <- cap * tanh(logits / cap); 0 = none */
+    float final_norm_gain;
+    const void* embed;         /* bf16 [vocab, width] */
+    const void* head;          /* bf16 [vocab, width] */
+    const ft_layer_desc* layers;
+} ft_layered_model;
+
+/* cfg: vocab, max_batch, max_batched_tokens, num_pages, max_context, max_sessions (= state slots), eos, debug_logit_rows
+ * are read; the Llama fields are ignored.  The descriptors are copied; the tensors stay owned by the caller. */
+ft_engine* ft_engine_create_layered(const ft_engine_config* cfg, const ft_layered_model* model);
+
+/* One step over GIVEN tokens (teacher forcing; replaying a recorded schedule).  Entry i appends counts[i] tokens to session
+ * session_keys[i] (created at its first entry) after what earlier steps left in its cache and state; `tokens` holds the
+ * entries' tokens one after the other.  All entries form ONE batch that goes through the same batch builder and forward
+ * pass as ft_engine_step: single tokens of running sessions as decode rows, the rest as prompt portions.  want_rows are
+ * indices into `tokens`; their logits -> HOST fp32 logits_out [n_want][vocab] (n_want <= debug_logit_rows).  Nothing is
+ * sampled.  The engine must have no request queued or running.  End a session with ft_engine_session_close. */
+int ft_engine_feed(ft_engine* e, int n_entries, const unsigned long long* session_keys, const int* counts,
+                   const int* tokens, int n_want, const int* want_rows, float* logits_out);
+/* Test hook (layered models): keep the residual stream after every layer of the following steps, and read it back as
+ * HOST fp32 [n_layers][rows][width] for the first `rows` token rows of the most recent step. */
+int ft_engine_debug_trail(ft_engine* e, int on);
+int ft_engine_debug_read_trail(ft_engine* e, float* host_out, int rows);
+
+/* ------------------------------------------------------------------------------------------
  * Kernel level — one entry point per kernel so each can be checked against the oracle.
  * ---------------------------------------------------------------------------------------- */
 
