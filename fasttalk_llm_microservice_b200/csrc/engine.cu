@@ -1450,10 +1450,15 @@ extern "C" int ft_engine_debug_read_trail(ft_engine* h, float* host_out, int row
 extern "C" void ft_engine_destroy(ft_engine* h) {
     if (!h) return;
     Engine* e = reinterpret_cast<Engine*>(h);
-    ft_engine_stop(h);
-    {   // a thread still blocked in ft_engine_wait (a daemon thread of the host at interpreter exit) leaves first
-        std::unique_lock<std::mutex> lk(e->mu);
+    {   // a thread still blocked in ft_engine_wait (a daemon thread of the host at interpreter exit) leaves first; the
+        // mark is set before the stepping thread stops, so that the waiter wakes to "destroyed" and not to "loop ended"
+        std::lock_guard<std::mutex> lk(e->mu);
         e->closing = true;
+        e->cv_out.notify_all();
+    }
+    ft_engine_stop(h);
+    {
+        std::unique_lock<std::mutex> lk(e->mu);
         e->cv_out.notify_all();
         e->cv_out.wait_for(lk, std::chrono::seconds(2), [&] { return e->waiters == 0; });
     }
