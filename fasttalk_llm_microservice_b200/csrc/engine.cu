@@ -181,6 +181,9 @@ struct Layered {
     float *hn = nullptr, *proj = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *b4 = nullptr, *beta = nullptr,
           *mix = nullptr, *act = nullptr, *eout = nullptr, *wts = nullptr, *xlast = nullptr;
     int *ids = nullptr, *seg = nullptr, *slot_token = nullptr, *slot_pos = nullptr;
+    void *pl_hi = nullptr, *pl_lo = nullptr;      // bf16 planes of a projection's input [t_max][k_max]
+    void *hn_hi = nullptr, *hn_lo = nullptr;      // bf16 planes of the normed layer input [t_max][width]
+    bool tensor = false;               // projections that tile run on the tensor cores (ft_layered_model.exact_f32 == 0)
     float* trail = nullptr;            // debug: residual stream after every layer [n_layers][t_max][width]
     bool trail_on = false;
 };
@@ -536,6 +539,39 @@ static int forward(Engine* e, const Batch& b) {
     return 0;
 }
 
+// A plain projection C[T][N] = A[T][K] W[N][K]^T.  With enough rows and shapes that tile, on the tensor cores: the fp32 input
+// as bf16 hi + lo planes (`hi` / `lo` if the producer already wrote them, else staged here), fp32 out.  Otherwise, and always
+// in the exact-fp32 form, the CUDA-core kernels.
+constexpr int kTensorMinRows = 17;
+static int dense(Engine* e, const float* A, const void* hi, const void* lo, const void* W, float* C, int T, int N, int K,
+                 float softcap = 0.f) {
+    Layered& L = *e->lay;
+    if (L.tensor && T >= kTensorMinRows && N % 128 == 0 && K % 64 == 0) {
+        if (!hi) {
+            FT_TRY(launch_to_planes(A, L.pl_hi, L.pl_lo, (size_t)T * K, e->stream));
+            e->st.kernel_launches++;
+            hi = L.pl_hi;
+            lo = L.pl_lo;
+        }
+        ft_gemm_epilogue ep = {};
+        ep.mode = FT_EPI_PARTIAL;
+        ep.out = C;
+        FT_TRY(ft_gemm_fused(W, hi, lo, N, T, K, 1, &ep, e->stream));
+        e->st.kernel_launches++;
+        if (softcap > 0.f) {
+            FT_TRY(launch_softcap(C, (size_t)T * N, softcap, e->stream));
+            e->st.kernel_launches++;
+        }
+        return 0;
+    }
+    LinearArgs a;
+    a.A = A; a.lda = K; a.W = (const __nv_bfloat16*)W; a.ldw = K; a.C = C; a.ldc = N; a.M = T; a.N = N; a.K = K;
+    if (softcap > 0.f) { a.epi = LIN_SOFTCAP; a.cap = softcap; }
+    FT_TRY(launch_linear(a, T, e->stream));
+    e->st.kernel_launches++;
+    return 0;
+}
+
 // Forward pass of a layered model.  Per layer: ONE projection of the normed input into all the parts that read it
 // (queries, latents or q/k/v, gates, low-rank inner products, residual gates, router logits), the mixer, the experts, and
 // one kernel that updates the residual stream and norms it for the next layer.
@@ -544,21 +580,18 @@ static int forward_layered(Engine* e, const Batch& b) {
     const ft_layered_model& M = L.m;
     StepMeta& m = e->meta;
     int* d = m.d;
-    const int T = b.T, W = M.width, ld = L.ld_proj;
+    const int T = b.T, W = M.width;
     cudaStream_t st = e->stream;
+    void* hn_hi = L.tensor && T >= kTensorMinRows ? L.hn_hi : nullptr;      // planes of the normed input, written by its producer
+    void* hn_lo = hn_hi ? L.hn_lo : nullptr;
     auto launched = [&](int n = 1) { e->st.kernel_launches += n; };
-    FT_TRY(launch_embed_norm(d + m.o_tokens, M.embed, e->resid, L.hn, T, W, M.eps, L.layers[0].d.norm_gain, st));
+    FT_TRY(launch_embed_norm(d + m.o_tokens, M.embed, e->resid, L.hn, hn_hi, hn_lo, T, W, M.eps, L.layers[0].d.norm_gain, st));
     launched();
     for (int l = 0; l < M.n_layers; ++l) {
         const LayeredLayer& ll = L.layers[l];
         const ft_layer_desc& c = ll.d;
-        {
-            LinearArgs a;
-            a.A = L.hn; a.lda = W; a.W = (const __nv_bfloat16*)c.w_in; a.ldw = W; a.C = L.proj; a.ldc = ld;
-            a.M = T; a.N = c.n_in; a.K = W;
-            FT_TRY(launch_linear(a, T, st));
-            launched();
-        }
+        const int ld = c.n_in;              // row stride of this layer's projection outputs
+        FT_TRY(dense(e, L.hn, hn_hi, hn_lo, c.w_in, L.proj, T, c.n_in, W));
         const float* mixed = nullptr;      // [T][heads * vdim], input of the output projection
         if (c.mixer == FT_MIXER_LATENT_ATTENTION) {
             float* cache = L.lat_cache + ll.cache_off;
@@ -602,13 +635,7 @@ static int forward_layered(Engine* e, const Batch& b) {
             launched(6);
             mixed = L.b4;
         }
-        {
-            LinearArgs a;
-            a.A = mixed; a.lda = c.heads * c.vdim; a.W = (const __nv_bfloat16*)c.w_o; a.ldw = c.heads * c.vdim;
-            a.C = L.mix; a.ldc = W; a.M = T; a.N = W; a.K = c.heads * c.vdim;
-            FT_TRY(launch_linear(a, T, st));
-            launched();
-        }
+        FT_TRY(dense(e, mixed, nullptr, nullptr, c.w_o, L.mix, T, W, c.heads * c.vdim));
         int top = 0;
         if (c.ff_kind == FT_FF_MOE) {
             top = c.top;
@@ -627,7 +654,7 @@ static int forward_layered(Engine* e, const Batch& b) {
         }
         const float gain_next = l + 1 < M.n_layers ? L.layers[l + 1].d.norm_gain : M.final_norm_gain;
         FT_TRY(launch_combine_norm(e->resid, L.hn, L.proj, ld, c.o_rg1, c.o_rg2, c.rg_bias, L.mix, L.eout, L.wts,
-                                   L.slot_pos, top, T, W, M.eps, gain_next, st));
+                                   L.slot_pos, top, T, W, M.eps, gain_next, hn_hi, hn_lo, st));
         launched();
         if (L.trail_on && L.trail)
             FT_CHECK_CUDA(cudaMemcpyAsync(L.trail + (size_t)l * e->t_max * W, e->resid, (size_t)T * W * 4,
@@ -640,12 +667,7 @@ static int forward_layered(Engine* e, const Batch& b) {
             launched();
             x = L.xlast;
         }
-        LinearArgs a;
-        a.A = x; a.lda = W; a.W = (const __nv_bfloat16*)M.head; a.ldw = W; a.C = e->logits; a.ldc = M.vocab;
-        a.M = b.n_logit_rows; a.N = M.vocab; a.K = W;
-        if (M.logit_softcap > 0.f) { a.epi = LIN_SOFTCAP; a.cap = M.logit_softcap; }
-        FT_TRY(launch_linear(a, b.n_logit_rows, st));
-        launched();
+        FT_TRY(dense(e, x, nullptr, nullptr, M.head, e->logits, b.n_logit_rows, M.vocab, W, M.logit_softcap));
     }
     return 0;
 }
@@ -1192,8 +1214,10 @@ static int engine_init_layered(Engine* e) {
         }
     }
     L.ld_proj = (n_in_max + 3) & ~3;
+    L.tensor = M.exact_f32 == 0;
     L.top_max = top_max;
     const size_t T = e->t_max, W = M.width;
+    const size_t rows_last_min = std::max<size_t>(e->logit_rows, 256);
     auto alloc = [&](void* pp, size_t bytes) -> int {
         void** p = reinterpret_cast<void**>(pp);
         FT_CHECK_CUDA(cudaMalloc(p, std::max<size_t>(bytes, 16)));
@@ -1205,6 +1229,13 @@ static int engine_init_layered(Engine* e) {
     FT_TRY(alloc(&e->resid, T * W * 4));
     FT_TRY(alloc(&L.hn, T * W * 4));
     FT_TRY(alloc(&L.proj, T * L.ld_proj * 4));
+    if (L.tensor) {
+        const size_t k_max = std::max(buf, W);
+        FT_TRY(alloc(&L.pl_hi, std::max<size_t>(T, rows_last_min) * k_max * 2));
+        FT_TRY(alloc(&L.pl_lo, std::max<size_t>(T, rows_last_min) * k_max * 2));
+        FT_TRY(alloc(&L.hn_hi, T * W * 2));
+        FT_TRY(alloc(&L.hn_lo, T * W * 2));
+    }
     FT_TRY(alloc(&L.b1, T * buf * 4));
     FT_TRY(alloc(&L.b2, T * buf * 4));
     FT_TRY(alloc(&L.b3, T * buf * 4));
@@ -1249,7 +1280,7 @@ static void engine_free(Engine* e) {
         cudaFree(L.lat_cache); cudaFree(L.state); cudaFree(L.hn); cudaFree(L.proj); cudaFree(L.b1); cudaFree(L.b2);
         cudaFree(L.b3); cudaFree(L.b4); cudaFree(L.beta); cudaFree(L.mix); cudaFree(L.act); cudaFree(L.eout);
         cudaFree(L.wts); cudaFree(L.xlast); cudaFree(L.ids); cudaFree(L.seg); cudaFree(L.slot_token);
-        cudaFree(L.slot_pos); cudaFree(L.trail);
+        cudaFree(L.slot_pos); cudaFree(L.trail); cudaFree(L.pl_hi); cudaFree(L.pl_lo); cudaFree(L.hn_hi); cudaFree(L.hn_lo);
         delete e->lay;
     }
     if (e->meta.h) cudaFreeHost(e->meta.h);

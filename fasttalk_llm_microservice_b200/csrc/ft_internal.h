@@ -109,11 +109,14 @@ struct LinearArgs {
 };
 // rows_bound: M when batched; an upper bound of seg[P] when grouped
 int launch_linear(const LinearArgs& a, int rows_bound, cudaStream_t stream);
-int launch_embed_norm(const int* tokens, const void* embed, float* x, float* hn, int T, int W, float eps, float gain,
-                      cudaStream_t stream);
+// hi / lo (may be null): the normed row once more as bf16 planes, the input form of the tensor-core projections
+int launch_embed_norm(const int* tokens, const void* embed, float* x, float* hn, void* hi, void* lo, int T, int W, float eps,
+                      float gain, cudaStream_t stream);
+int launch_to_planes(const float* x, void* hi, void* lo, size_t n, cudaStream_t stream);
+int launch_softcap(float* x, size_t n, float cap, cudaStream_t stream);
 int launch_combine_norm(float* x, float* hn, const float* proj, int ldp, int o_rg1, int o_rg2, const float* rg_bias,
                         const float* mix, const float* eout, const float* wt, const int* slot_pos, int top, int T, int W,
-                        float eps, float gain, cudaStream_t stream);
+                        float eps, float gain, void* hi, void* lo, cudaStream_t stream);
 int launch_gather_rows(const float* src, const int* idx, float* dst, int n, int W, cudaStream_t stream);
 int launch_latent_write(const float* proj, int ldp, int o_dkv, const float* w, float* cache, const int* positions,
                         const int* seq_rows, const int* page_table, int max_pages, int rank, float eps, int T,

@@ -18,6 +18,8 @@
 #include "common.cuh"
 #include "ft_internal.h"
 
+#include <algorithm>
+
 namespace ft {
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
@@ -253,11 +255,45 @@ int launch_linear(const LinearArgs& a, int rows_bound, cudaStream_t stream) {
     return 0;
 }
 
+// ------------------------------------------------------------------ bf16 planes for the tensor-core projections
+// v = hi + lo with hi = bf16(v), lo = bf16(v - hi): the tcgen05 GEMM multiplies both planes into one fp32 accumulator, which
+// keeps about 16 mantissa bits of an fp32 activation.
+__device__ __forceinline__ void store_planes(__nv_bfloat16* hi, __nv_bfloat16* lo, size_t i, float v) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    hi[i] = h;
+    lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+}
+
+__global__ void to_planes_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+                                 size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        store_planes(hi, lo, i, x[i]);
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] / cap);
+}
+
+int launch_to_planes(const float* x, void* hi, void* lo, size_t n, cudaStream_t stream) {
+    const int blocks = (int)std::min<size_t>((n + 255) / 256, 148 * 16);
+    to_planes_kernel<<<blocks, 256, 0, stream>>>(x, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, n);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+int launch_softcap(float* x, size_t n, float cap, cudaStream_t stream) {
+    const int blocks = (int)std::min<size_t>((n + 255) / 256, 148 * 16);
+    softcap_kernel<<<blocks, 256, 0, stream>>>(x, n, cap);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
 // ------------------------------------------------------------------ embedding / residual update, fused with the next norm
 // hn[t] = x[t] / sqrt(mean(x[t]^2) + eps) * gain, the gain being one number.
 __global__ void __launch_bounds__(256)
 embed_norm_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ embed, float* __restrict__ x,
-                  float* __restrict__ hn, int W, float eps, float gain) {
+                  float* __restrict__ hn, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo, int W, float eps,
+                  float gain) {
     __shared__ float red[33];
     const int t = blockIdx.x;
     const __nv_bfloat16* e = embed + (size_t)tokens[t] * W;
@@ -269,7 +305,11 @@ embed_norm_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restric
     }
     ss = block_sum(ss, red);
     const float r = gain / sqrtf(ss / (float)W + eps);
-    for (int c = threadIdx.x; c < W; c += blockDim.x) hn[(size_t)t * W + c] = __bfloat162float(e[c]) * r;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = __bfloat162float(e[c]) * r;
+        hn[(size_t)t * W + c] = v;
+        if (hi) store_planes(hi, lo, (size_t)t * W + c, v);
+    }
 }
 
 // x[t] += sigmoid(rg1[t] + b1) * mix[t] + sigmoid(rg2[t] + b2) * sum_k wt[t, k] * eout[slot_pos[t, k]]   (feed-forward
@@ -278,7 +318,7 @@ __global__ void __launch_bounds__(256)
 combine_norm_kernel(float* __restrict__ x, float* __restrict__ hn, const float* __restrict__ proj, int ldp, int o_rg1,
                     int o_rg2, const float* __restrict__ rg_bias, const float* __restrict__ mix,
                     const float* __restrict__ eout, const float* __restrict__ wt, const int* __restrict__ slot_pos,
-                    int top, int W, float eps, float gain) {
+                    int top, int W, float eps, float gain, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
     __shared__ float red[33];
     extern __shared__ float row[];
     const int t = blockIdx.x;
@@ -299,7 +339,11 @@ combine_norm_kernel(float* __restrict__ x, float* __restrict__ hn, const float* 
     }
     ss = block_sum(ss, red);
     const float r = gain / sqrtf(ss / (float)W + eps);
-    for (int c = threadIdx.x; c < W; c += blockDim.x) hn[(size_t)t * W + c] = row[c] * r;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = row[c] * r;
+        hn[(size_t)t * W + c] = v;
+        if (hi) store_planes(hi, lo, (size_t)t * W + c, v);
+    }
 }
 
 // rows of the normed stream that the head reads: out[i] = hn[idx[i]]
@@ -309,17 +353,18 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __r
     for (int c = threadIdx.x; c < W; c += blockDim.x) dst[(size_t)i * W + c] = s[c];
 }
 
-int launch_embed_norm(const int* tokens, const void* embed, float* x, float* hn, int T, int W, float eps, float gain,
-                      cudaStream_t stream) {
-    embed_norm_kernel<<<T, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)embed, x, hn, W, eps, gain);
+int launch_embed_norm(const int* tokens, const void* embed, float* x, float* hn, void* hi, void* lo, int T, int W, float eps,
+                      float gain, cudaStream_t stream) {
+    embed_norm_kernel<<<T, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)embed, x, hn, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo,
+                                             W, eps, gain);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
 int launch_combine_norm(float* x, float* hn, const float* proj, int ldp, int o_rg1, int o_rg2, const float* rg_bias,
                         const float* mix, const float* eout, const float* wt, const int* slot_pos, int top, int T, int W,
-                        float eps, float gain, cudaStream_t stream) {
+                        float eps, float gain, void* hi, void* lo, cudaStream_t stream) {
     combine_norm_kernel<<<T, 256, (size_t)W * 4, stream>>>(x, hn, proj, ldp, o_rg1, o_rg2, rg_bias, mix, eout, wt, slot_pos,
-                                                          top, W, eps, gain);
+                                                          top, W, eps, gain, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

@@ -40,6 +40,7 @@ class EngineLimits:
     max_sessions: int = 0
     use_pdl: bool = True
     decode_prefill_cap: int = 0         # prompt tokens per step while sequences decode: 0 = 896, < 0 = uncapped
+    exact_f32: bool = False             # layered models: every product in true fp32 instead of tensor-core projections
     prefill_planes: int = 0             # large prefill GEMMs: 0 = default, 1 = bf16 hi only, 2 = bf16 hi + lo, 3 = one fp16 plane x fp16 weight copies
     debug_logit_rows: int = 0
 
@@ -111,7 +112,7 @@ class Engine:
         if self.tp_size > 1:
             raise N.NativeError("tensor parallelism is built for the Llama models only")
         self.spec = spec
-        model, self._keep = pack_layered(spec, weights, self.device)
+        model, self._keep = pack_layered(spec, weights, self.device, exact_f32=lim.exact_f32)
         pages_per_ctx = -(-lim.max_context // 64)
         num_pages = lim.num_pages or int(lim.max_batch * pages_per_ctx * 1.25) + 8
         cfg = N.EngineConfig()

@@ -222,25 +222,27 @@ class LayeredModel(C.Structure):
     _fields_ = [
         ("width", C.c_int), ("vocab", C.c_int), ("n_layers", C.c_int),
         ("eps", C.c_float), ("logit_softcap", C.c_float), ("final_norm_gain", C.c_float),
-        ("embed", C.c_void_p), ("head", C.c_void_p), ("layers", C.POINTER(LayerDesc)),
+        ("embed", C.c_void_p), ("head", C.c_void_p), ("layers", C.POINTER(LayerDesc)), ("exact_f32", C.c_int),
     ]
 
 
 def _stack_inputs(parts: List[Tuple[str, torch.Tensor]], width: int, device) -> Tuple[torch.Tensor, Dict[str, int]]:
     """Projections that read the same input, one under the other; every part starts on a multiple of four rows (the
-    kernels read its output columns four at a time), the gaps are zero rows."""
+    kernels read its output columns four at a time) and the whole is a multiple of 128 rows (the tensor-core GEMM's
+    tile); the gaps are zero rows."""
     offs, rows = {}, 0
     for name, t in parts:
         rows = (rows + 3) & ~3
         offs[name] = rows
         rows += t.shape[0]
+    rows = (rows + 127) & ~127
     out = torch.zeros(rows, width, dtype=torch.bfloat16, device=device)
     for name, t in parts:
         out[offs[name]:offs[name] + t.shape[0]] = t
     return out, offs
 
 
-def pack(spec: LayeredSpec, w: Dict[str, torch.Tensor], device) -> Tuple[LayeredModel, list]:
+def pack(spec: LayeredSpec, w: Dict[str, torch.Tensor], device, exact_f32: bool = False) -> Tuple[LayeredModel, list]:
     """Device arrays in the engine's layout + the descriptor structs.  Returns (model, keepalive): the engine borrows
     the pointers, so `keepalive` has to live as long as the engine."""
     keep: list = []
@@ -313,5 +315,6 @@ def pack(spec: LayeredSpec, w: Dict[str, torch.Tensor], device) -> Tuple[Layered
     model.embed = dev(w["embed"]).data_ptr()
     model.head = dev(w["head"]).data_ptr()
     model.layers = C.cast(descs, C.POINTER(LayerDesc))
+    model.exact_f32 = int(exact_f32)
     keep.append(descs)
     return model, keep

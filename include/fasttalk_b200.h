@@ -227,6 +227,10 @@ typedef struct {
     const void* embed;         /* bf16 [vocab, width] */
     const void* head;          /* bf16 [vocab, width] */
     const ft_layer_desc* layers;
+    int exact_f32;             /* 1: every product in true fp32 (CUDA-core kernels only).  0: the serving form — projections
+                                  of more than a few rows whose shapes tile (rows of W a multiple of 128, columns of 64) run on
+                                  the tensor cores (tcgen05) from bf16 hi + lo planes of the fp32 activations with fp32
+                                  accumulation; norms, scores, softmax, router, recurrence and residual stay fp32 */
 } ft_layered_model;
 
 /* cfg: vocab, max_batch, max_batched_tokens, num_pages, max_context, max_sessions (= state slots), eos, debug_logit_rows
