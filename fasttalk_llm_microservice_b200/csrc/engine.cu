@@ -179,7 +179,7 @@ struct Layered {
     int n_stateful = 0;                // layers whose mixer carries state from token to token
     int ld_proj = 0, top_max = 0;
     float *hn = nullptr, *proj = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *b4 = nullptr, *beta = nullptr,
-          *mix = nullptr, *act = nullptr, *eout = nullptr, *wts = nullptr, *xlast = nullptr;
+          *attn_part = nullptr, *mix = nullptr, *act = nullptr, *eout = nullptr, *wts = nullptr, *xlast = nullptr;
     int *ids = nullptr, *seg = nullptr, *slot_token = nullptr, *slot_pos = nullptr;
     void *pl_hi = nullptr, *pl_lo = nullptr;      // bf16 planes of a projection's input [t_max][k_max]
     void *hn_hi = nullptr, *hn_lo = nullptr;      // bf16 planes of the normed layer input [t_max][width]
@@ -603,7 +603,7 @@ static int forward_layered(Engine* e, const Batch& b) {
             a.C = L.b1; a.ldc = c.heads * c.kv_rank; a.c_col_stride = c.kv_rank;
             a.M = T; a.N = c.kv_rank; a.K = c.dim; a.P = c.heads;
             FT_TRY(launch_linear(a, T, st));
-            FT_TRY(launch_latent_attn(L.b1, cache, L.proj, ld, c.o_gate, L.b2, d + m.o_pos, d + m.o_rows, d + m.o_pt,
+            FT_TRY(launch_latent_attn(L.b1, cache, L.proj, ld, c.o_gate, L.b2, L.attn_part, d + m.o_pos, d + m.o_rows, d + m.o_pt,
                                       e->max_pages, c.heads, c.kv_rank, c.scale, T, st));
             LinearArgs v;                   // values out of latent space: o_h = W_uv_h (sum_j p_j c_j)
             v.A = L.b2; v.lda = c.heads * c.kv_rank; v.a_col_stride = c.kv_rank;
@@ -1173,7 +1173,7 @@ static int engine_init_layered(Engine* e) {
 
     // sizes over all layers; places of each layer in the latent cache and in a state slot
     size_t cache_floats = 0, buf = 1, act_cols = 1;
-    int n_in_max = 1, top_max = 1, heads_max = 1;
+    int n_in_max = 1, top_max = 1, heads_max = 1, rank_max = 0;
     for (int l = 0; l < M.n_layers; ++l) {
         LayeredLayer& ll = L.layers[l];
         const ft_layer_desc& d = ll.d;
@@ -1188,6 +1188,7 @@ static int engine_init_layered(Engine* e) {
             ll.cache_off = cache_floats;
             cache_floats += (size_t)c.num_pages * kKvTile * d.kv_rank;
             buf = std::max(buf, (size_t)d.heads * d.kv_rank);
+            rank_max = std::max(rank_max, d.kv_rank);
         } else if (d.mixer == FT_MIXER_CHANNEL_DELTA) {
             FT_REQUIRE(d.kv_heads >= 1 && d.heads % d.kv_heads == 0 && d.conv >= 1 && d.rank_a >= 1 && d.rank_g >= 1 &&
                            d.conv_w && d.w_a2 && d.w_g2 && d.dt_bias && d.a_log && d.out_norm && d.o_q >= 0 &&
@@ -1241,6 +1242,7 @@ static int engine_init_layered(Engine* e) {
     FT_TRY(alloc(&L.b3, T * buf * 4));
     FT_TRY(alloc(&L.b4, T * buf * 4));
     FT_TRY(alloc(&L.beta, T * heads_max * 4));
+    if (rank_max > 0) FT_TRY(alloc(&L.attn_part, (size_t)kLatentSplitPairs * kLatentMaxSplits * (rank_max + 2) * 4));
     FT_TRY(alloc(&L.mix, T * W * 4));
     FT_TRY(alloc(&L.act, T * top_max * act_cols * 4));
     FT_TRY(alloc(&L.eout, T * top_max * W * 4));
@@ -1278,7 +1280,7 @@ static void engine_free(Engine* e) {
     if (e->lay) {
         Layered& L = *e->lay;
         cudaFree(L.lat_cache); cudaFree(L.state); cudaFree(L.hn); cudaFree(L.proj); cudaFree(L.b1); cudaFree(L.b2);
-        cudaFree(L.b3); cudaFree(L.b4); cudaFree(L.beta); cudaFree(L.mix); cudaFree(L.act); cudaFree(L.eout);
+        cudaFree(L.b3); cudaFree(L.b4); cudaFree(L.beta); cudaFree(L.attn_part); cudaFree(L.mix); cudaFree(L.act); cudaFree(L.eout);
         cudaFree(L.wts); cudaFree(L.xlast); cudaFree(L.ids); cudaFree(L.seg); cudaFree(L.slot_token);
         cudaFree(L.slot_pos); cudaFree(L.trail); cudaFree(L.pl_hi); cudaFree(L.pl_lo); cudaFree(L.hn_hi); cudaFree(L.hn_lo);
         delete e->lay;

@@ -121,7 +121,11 @@ int launch_gather_rows(const float* src, const int* idx, float* dst, int n, int 
 int launch_latent_write(const float* proj, int ldp, int o_dkv, const float* w, float* cache, const int* positions,
                         const int* seq_rows, const int* page_table, int max_pages, int rank, float eps, int T,
                         cudaStream_t stream);
-int launch_latent_attn(const float* qlat, const float* cache, const float* proj, int ldp, int o_gate, float* out,
+// With fewer than kLatentSplitPairs (token, head) pairs in a step the keys of each are cut into up to kLatentMaxSplits
+// shares that run side by side; `part` then holds pairs x shares x (kv_rank + 2) floats (null: never split).
+constexpr int kLatentSplitPairs = 2048, kLatentMaxSplits = 8;
+int latent_attn_splits(int T, int H);
+int launch_latent_attn(const float* qlat, const float* cache, const float* proj, int ldp, int o_gate, float* out, float* part,
                        const int* positions, const int* seq_rows, const int* page_table, int max_pages, int H, int rank,
                        float scale, int T, cudaStream_t stream);
 struct DeltaArgs {

@@ -150,8 +150,8 @@ __global__ void __launch_bounds__(LTHREADS) linear_tile_kernel(LinearArgs a) {
 
 // ------------------------------------------------------------------ linear: few rows (decode)
 // One warp per output column (per pair of columns with the SwiGLU epilogue) and up to LROWS rows: the weights are read
-// once, 8 bytes per lane per load; the rows come from L1 / L2.
-constexpr int LROWS = 8;
+// once per block of LROWS rows, 16 bytes per lane per load; the rows come from L1 / L2.
+constexpr int LROWS = 16;
 
 __global__ void __launch_bounds__(256) linear_rows_kernel(LinearArgs a) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -168,8 +168,8 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(LinearArgs a) {
     const int n = pair ? 2 * warp : warp;
     const __nv_bfloat16* w0 = W + (size_t)n * a.ldw;
     const __nv_bfloat16* w1 = w0 + a.ldw;
-    const bool vec = (a.K & 3) == 0 && (a.ldw & 3) == 0 && (a.lda & 3) == 0 && (a.a_col_stride & 3) == 0 &&
-                     ((a.w_stride & 3) == 0);
+    const bool vec = (a.K & 7) == 0 && (a.ldw & 7) == 0 && (a.lda & 3) == 0 && (a.a_col_stride & 3) == 0 &&
+                     (a.w_stride & 7) == 0 && ((uintptr_t)a.A & 15) == 0 && ((uintptr_t)a.W & 15) == 0;
     for (int rb = r0; rb < r1; rb += LROWS) {
         const int nr = min(LROWS, r1 - rb);
         const float* ar[LROWS];
@@ -182,23 +182,27 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(LinearArgs a) {
 #pragma unroll
         for (int i = 0; i < LROWS; ++i) acc0[i] = acc1[i] = 0.f;
         if (vec) {
-            for (int k = lane * 4; k < a.K; k += 128) {
-                const uint2 t = *reinterpret_cast<const uint2*>(w0 + k);
-                const float wa[4] = {bf16_lo(t.x), bf16_hi(t.x), bf16_lo(t.y), bf16_hi(t.y)};
-                float wb[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int k = lane * 8; k < a.K; k += 256) {
+                const uint4 t = __ldg(reinterpret_cast<const uint4*>(w0 + k));
+                const float wa[8] = {bf16_lo(t.x), bf16_hi(t.x), bf16_lo(t.y), bf16_hi(t.y),
+                                     bf16_lo(t.z), bf16_hi(t.z), bf16_lo(t.w), bf16_hi(t.w)};
+                float wb[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                 if (pair) {
-                    const uint2 u = *reinterpret_cast<const uint2*>(w1 + k);
+                    const uint4 u = __ldg(reinterpret_cast<const uint4*>(w1 + k));
                     wb[0] = bf16_lo(u.x); wb[1] = bf16_hi(u.x); wb[2] = bf16_lo(u.y); wb[3] = bf16_hi(u.y);
+                    wb[4] = bf16_lo(u.z); wb[5] = bf16_hi(u.z); wb[6] = bf16_lo(u.w); wb[7] = bf16_hi(u.w);
                 }
 #pragma unroll
                 for (int i = 0; i < LROWS; ++i) {
                     if (i < nr) {
-                        const float4 x = *reinterpret_cast<const float4*>(ar[i] + k);
-                        acc0[i] = fmaf(x.x, wa[0], acc0[i]); acc0[i] = fmaf(x.y, wa[1], acc0[i]);
-                        acc0[i] = fmaf(x.z, wa[2], acc0[i]); acc0[i] = fmaf(x.w, wa[3], acc0[i]);
+                        const float4 x0 = *reinterpret_cast<const float4*>(ar[i] + k);
+                        const float4 x1 = *reinterpret_cast<const float4*>(ar[i] + k + 4);
+                        const float xa[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc0[i] = fmaf(xa[e], wa[e], acc0[i]);
                         if (pair) {
-                            acc1[i] = fmaf(x.x, wb[0], acc1[i]); acc1[i] = fmaf(x.y, wb[1], acc1[i]);
-                            acc1[i] = fmaf(x.z, wb[2], acc1[i]); acc1[i] = fmaf(x.w, wb[3], acc1[i]);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) acc1[i] = fmaf(xa[e], wb[e], acc1[i]);
                         }
                     }
                 }
@@ -236,7 +240,7 @@ int launch_linear(const LinearArgs& a, int rows_bound, cudaStream_t stream) {
     FT_REQUIRE(a.K >= 1 && a.P >= 1, "linear: bad sizes");
     FT_REQUIRE(a.epi != LIN_SWIGLU_PAIR || (a.N & 1) == 0, "linear: the paired epilogue needs an even number of rows");
     // few rows per problem: one warp per output column, the weights stream once
-    const bool few = a.seg ? rows_bound <= 2 * LROWS : rows_bound <= LROWS;
+    const bool few = a.seg ? rows_bound <= 4 * LROWS : rows_bound <= 2 * LROWS;
     if (few) {
         const int cols = a.epi == LIN_SWIGLU_PAIR ? a.N / 2 : a.N;
         dim3 grid((cols + 7) / 8, a.P);
@@ -394,15 +398,20 @@ latent_write_kernel(const float* __restrict__ proj, int ldp, int o_dkv, const fl
     for (int c = threadIdx.x; c < rank; c += blockDim.x) dst[c] = raw[c] * r * w[c];
 }
 
-// One warp per (token, head): the query in latent space stays in registers (NR values per lane), keys = values = the
-// cached latents of positions 0..pos, online softmax in fp32.  The head's result is scaled by its output gate
-// sigmoid(gate logit): the value expansion that follows is linear, so gating before it is the same.
-template <int NR>
+// One warp per (token, head, key range): the query in latent space stays in registers (NR values per lane), keys = values =
+// the cached latents, online softmax in fp32.  Keys are taken KB at a time: their rows are all requested before the first
+// is used and the KB score reductions interleave, so the loop waits for memory once per block instead of once per key.
+// With n_split == 1 the warp finishes its (token, head): divides by the softmax sum and scales by the head's output gate
+// sigmoid(gate logit) — the value expansion that follows is linear, so gating before it is the same.  With n_split > 1
+// (few tokens: decode) it covers the s-th share of the keys and leaves (max, sum, unnormalised result) for the merge.
+template <int NR, int KB>
 __global__ void __launch_bounds__(128)
 latent_attn_kernel(const float* __restrict__ qlat, const float* __restrict__ cache, const float* __restrict__ proj, int ldp,
-                   int o_gate, float* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_rows,
-                   const int* __restrict__ page_table, int max_pages, int H, int rank, float scale, int n_pairs) {
+                   int o_gate, float* __restrict__ out, float* __restrict__ part, const int* __restrict__ positions,
+                   const int* __restrict__ seq_rows, const int* __restrict__ page_table, int max_pages, int H, int rank,
+                   float scale, int n_pairs, int n_split) {
     const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int split = blockIdx.y;
     if (pair >= n_pairs) return;
     const int t = pair / H, h = pair % H;
     const float* q = qlat + ((size_t)t * H + h) * rank;
@@ -413,29 +422,66 @@ latent_attn_kernel(const float* __restrict__ qlat, const float* __restrict__ cac
         qr[i] = c < rank ? q[c] * scale : 0.f;
         acc[i] = 0.f;
     }
-    const int pos = positions[t];
+    const int n_keys = positions[t] + 1;
+    int j_lo = 0, j_hi = n_keys;
+    if (n_split > 1) {          // shares of whole pages
+        const int share = ((n_keys + n_split - 1) / n_split + kKvTile - 1) / kKvTile * kKvTile;
+        j_lo = min(split * share, n_keys);
+        j_hi = min(j_lo + share, n_keys);
+    }
     const int* pt = page_table + (size_t)seq_rows[t] * max_pages;
     float m = -INFINITY, l = 0.f;
-    for (int j0 = 0; j0 <= pos; j0 += kKvTile) {
-        const float* pg = cache + (size_t)pt[j0 / kKvTile] * kKvTile * rank;
-        const int nj = min(kKvTile, pos + 1 - j0);
-        for (int j = 0; j < nj; ++j) {
-            const float* c = pg + (size_t)j * rank;
-            float cv[NR], s = 0.f;
+    for (int j0 = j_lo; j0 < j_hi; j0 += KB) {
+        float cv[KB][NR], sc[KB];
+#pragma unroll
+        for (int b = 0; b < KB; ++b) {
+            const int j = min(j0 + b, j_hi - 1);
+            const float* c = cache + ((size_t)pt[j / kKvTile] * kKvTile + j % kKvTile) * rank;
 #pragma unroll
             for (int i = 0; i < NR; ++i) {
                 const int cc = lane + 32 * i;
-                cv[i] = cc < rank ? c[cc] : 0.f;
-                s = fmaf(qr[i], cv[i], s);
+                cv[b][i] = cc < rank ? c[cc] : 0.f;
             }
-            s = warp_sum(s);
-            const float mn = fmaxf(m, s);
-            const float corr = expf(m - mn), pw = expf(s - mn);
-            l = l * corr + pw;
-#pragma unroll
-            for (int i = 0; i < NR; ++i) acc[i] = fmaf(pw, cv[i], acc[i] * corr);
-            m = mn;
         }
+#pragma unroll
+        for (int b = 0; b < KB; ++b) {
+            float x = 0.f;
+#pragma unroll
+            for (int i = 0; i < NR; ++i) x = fmaf(qr[i], cv[b][i], x);
+            sc[b] = x;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int b = 0; b < KB; ++b) sc[b] += __shfl_xor_sync(0xffffffffu, sc[b], o);
+        float mn = m;
+#pragma unroll
+        for (int b = 0; b < KB; ++b) {
+            if (j0 + b >= j_hi) sc[b] = -INFINITY;
+            mn = fmaxf(mn, sc[b]);
+        }
+        const float corr = expf(m - mn);
+        l *= corr;
+#pragma unroll
+        for (int i = 0; i < NR; ++i) acc[i] *= corr;
+#pragma unroll
+        for (int b = 0; b < KB; ++b) {
+            const float pw = expf(sc[b] - mn);          // 0 for the padding of the last block
+            l += pw;
+#pragma unroll
+            for (int i = 0; i < NR; ++i) acc[i] = fmaf(pw, cv[b][i], acc[i]);
+        }
+        m = mn;
+    }
+    if (n_split > 1) {
+        float* p = part + ((size_t)pair * n_split + split) * (rank + 2);
+        if (lane == 0) { p[0] = m; p[1] = l; }
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int c = lane + 32 * i;
+            if (c < rank) p[2 + c] = acc[i];
+        }
+        return;
     }
     const float g = sigmoid_exact(proj[(size_t)t * ldp + o_gate + h]) / l;
     float* o = out + ((size_t)t * H + h) * rank;
@@ -443,6 +489,32 @@ latent_attn_kernel(const float* __restrict__ qlat, const float* __restrict__ cac
     for (int i = 0; i < NR; ++i) {
         const int c = lane + 32 * i;
         if (c < rank) o[c] = acc[i] * g;
+    }
+}
+
+// The shares of one (token, head) put together: one warp each.
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const float* __restrict__ part, const float* __restrict__ proj, int ldp, int o_gate, float* __restrict__ out,
+                    int H, int rank, int n_pairs, int n_split) {
+    const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (pair >= n_pairs) return;
+    const float* p = part + (size_t)pair * n_split * (rank + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < n_split; ++s) m = fmaxf(m, p[(size_t)s * (rank + 2)]);
+    float l = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+        const float ms = p[(size_t)s * (rank + 2)];
+        if (ms > -INFINITY) l += p[(size_t)s * (rank + 2) + 1] * expf(ms - m);
+    }
+    const int t = pair / H, h = pair % H;
+    const float g = sigmoid_exact(proj[(size_t)t * ldp + o_gate + h]) / l;
+    for (int c = lane; c < rank; c += 32) {
+        float a = 0.f;
+        for (int s = 0; s < n_split; ++s) {
+            const float ms = p[(size_t)s * (rank + 2)];
+            if (ms > -INFINITY) a = fmaf(p[(size_t)s * (rank + 2) + 2 + c], expf(ms - m), a);
+        }
+        out[(size_t)pair * rank + c] = a * g;
     }
 }
 
@@ -454,22 +526,33 @@ int launch_latent_write(const float* proj, int ldp, int o_dkv, const float* w, f
     return 0;
 }
 
-int launch_latent_attn(const float* qlat, const float* cache, const float* proj, int ldp, int o_gate, float* out,
+int latent_attn_splits(int T, int H) {
+    const int pairs = T * H;
+    if (pairs >= kLatentSplitPairs) return 1;
+    return std::max(1, std::min(kLatentMaxSplits, kLatentSplitPairs / std::max(pairs, 1)));
+}
+
+int launch_latent_attn(const float* qlat, const float* cache, const float* proj, int ldp, int o_gate, float* out, float* part,
                        const int* positions, const int* seq_rows, const int* page_table, int max_pages, int H, int rank,
                        float scale, int T, cudaStream_t stream) {
     const int n_pairs = T * H;
-    const dim3 grid((n_pairs + 3) / 4);
-#define FT_LAT(NR_)                                                                                                      \
-    latent_attn_kernel<NR_><<<grid, 128, 0, stream>>>(qlat, cache, proj, ldp, o_gate, out, positions, seq_rows, page_table, \
-                                                      max_pages, H, rank, scale, n_pairs)
-    if (rank <= 32) FT_LAT(1);
-    else if (rank <= 64) FT_LAT(2);
-    else if (rank <= 128) FT_LAT(4);
-    else if (rank <= 256) FT_LAT(8);
-    else if (rank <= 512) FT_LAT(16);
-    else { FT_REQUIRE(rank <= 1024, "latent attention: latent size %d is beyond 1024", rank); FT_LAT(32); }
+    const int n_split = part ? latent_attn_splits(T, H) : 1;
+    const dim3 grid((n_pairs + 3) / 4, n_split);
+#define FT_LAT(NR_, KB_)                                                                                                   \
+    latent_attn_kernel<NR_, KB_><<<grid, 128, 0, stream>>>(qlat, cache, proj, ldp, o_gate, out, part, positions, seq_rows, \
+                                                           page_table, max_pages, H, rank, scale, n_pairs, n_split)
+    if (rank <= 32) FT_LAT(1, 8);
+    else if (rank <= 64) FT_LAT(2, 8);
+    else if (rank <= 128) FT_LAT(4, 8);
+    else if (rank <= 256) FT_LAT(8, 4);
+    else if (rank <= 512) FT_LAT(16, 4);
+    else { FT_REQUIRE(rank <= 1024, "latent attention: latent size %d is beyond 1024", rank); FT_LAT(32, 2); }
 #undef FT_LAT
     FT_CHECK_CUDA(cudaGetLastError());
+    if (n_split > 1) {
+        latent_merge_kernel<<<(n_pairs + 3) / 4, 128, 0, stream>>>(part, proj, ldp, o_gate, out, H, rank, n_pairs, n_split);
+        FT_CHECK_CUDA(cudaGetLastError());
+    }
     return 0;
 }
 
@@ -540,64 +623,98 @@ __global__ void delta_tail_kernel(DeltaArgs a, int n_req) {
     for (int i = 0; i < keep; ++i) tail[i] = v[i];
 }
 
-// The recurrence, one CTA per (request, head), one thread per column of the state S [dim][vdim]: per token
+// The recurrence, one CTA per (request, head).  Per token
 //   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
-// is local to a column, so no thread talks to another; q, k, g, v of a few tokens are staged in shared memory at a time.
+// is local to a column of the state S [dim][vdim].  Four neighbouring lanes share a column, each holding every fourth key
+// channel of it in registers (DPT values), so the two sums over key channels are a short chain plus two shuffles.
+// q, k, g, v, beta of DCHUNK tokens at a time are copied into shared memory asynchronously (cp.async), one chunk ahead
+// of the one being computed.
 constexpr int DCHUNK = 8;
-template <int DMAX>
-__global__ void __launch_bounds__(256)
+__device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+template <int DPT, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 delta_rule_kernel(DeltaArgs a) {
     extern __shared__ float sh[];
-    const int req = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+    const int req = blockIdx.x, h = blockIdx.y;
+    const int j = threadIdx.x >> 2, part = threadIdx.x & 3;      // column, and which quarter of the key channels
     const int kh = h / (a.heads / a.kvh);
     const int row0 = a.req_start[req], n = a.req_start[req + 1] - row0;
     const int dim = a.dim, vdim = a.vdim;
-    const int qk = a.kvh * dim, ch = 2 * qk + a.heads * vdim;
+    const int qk = a.kvh * dim, ch = 2 * qk + a.heads * vdim, hd = a.heads * dim;
     float* S = a.state + (size_t)a.req_slot[req] * a.slot_stride + a.s_off + (size_t)h * dim * vdim;
-    float s[DMAX];
     const bool live = j < vdim;
     const bool fresh = a.req_pos0[req] == 0;
+    float s[DPT];
 #pragma unroll
-    for (int d = 0; d < DMAX; ++d) s[d] = (live && !fresh && d < dim) ? S[(size_t)d * vdim + j] : 0.f;
-    // shared: per staged token  q[dim] k[dim] g[dim] v[vdim] beta
+    for (int i = 0; i < DPT; ++i) {
+        const int d = 4 * i + part;
+        s[i] = (live && !fresh && d < dim) ? S[(size_t)d * vdim + j] : 0.f;
+    }
+    // shared: two buffers of DCHUNK tokens, per token  q[dim] k[dim] g[dim] v[vdim] beta
     const int per = 3 * dim + vdim + 1;
-    for (int c0 = 0; c0 < n; c0 += DCHUNK) {
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    auto stage = [&](int c0, float* buf) {
         const int nc = min(DCHUNK, n - c0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < nc * per; i += blockDim.x) {
-            const int tt = i / per, e = i % per;
+        for (int tt = wid; tt < nc; tt += nw) {          // a warp per token
             const size_t t = row0 + c0 + tt;
-            float v;
-            if (e < dim) v = a.qkv[t * ch + (size_t)kh * dim + e];
-            else if (e < 2 * dim) v = a.qkv[t * ch + qk + (size_t)kh * dim + (e - dim)];
-            else if (e < 3 * dim) v = a.decay[t * ((size_t)a.heads * dim) + (size_t)h * dim + (e - 2 * dim)];
-            else if (e < 3 * dim + vdim) v = a.qkv[t * ch + 2 * qk + (size_t)h * vdim + (e - 3 * dim)];
-            else v = a.beta[t * a.heads + h];
-            sh[i] = v;
-        }
-        __syncthreads();
-        if (live) {
-            for (int tt = 0; tt < nc; ++tt) {
-                const float* q = sh + (size_t)tt * per;
-                const float* k = q + dim;
-                const float* g = k + dim;
-                float dot = 0.f;
-#pragma unroll
-                for (int d = 0; d < DMAX; ++d)
-                    if (d < dim) { s[d] *= g[d]; dot = fmaf(s[d], k[d], dot); }
-                const float u = g[dim + vdim] * (g[dim + j] - dot);
-                float o = 0.f;
-#pragma unroll
-                for (int d = 0; d < DMAX; ++d)
-                    if (d < dim) { s[d] = fmaf(k[d], u, s[d]); o = fmaf(s[d], q[d], o); }
-                a.o[(size_t)(row0 + c0 + tt) * ((size_t)a.heads * vdim) + (size_t)h * vdim + j] = o;
+            float* dst = buf + (size_t)tt * per;
+            const float* q = a.qkv + t * ch + (size_t)kh * dim;
+            const float* g = a.decay + t * hd + (size_t)h * dim;
+            const float* v = a.qkv + t * ch + 2 * qk + (size_t)h * vdim;
+            for (int e = lane; e < dim; e += 32) {
+                cp_async4(dst + e, q + e);
+                cp_async4(dst + dim + e, q + qk + e);
+                cp_async4(dst + 2 * dim + e, g + e);
             }
+            for (int e = lane; e < vdim; e += 32) cp_async4(dst + 3 * dim + e, v + e);
+            if (lane == 0) cp_async4(dst + 3 * dim + vdim, a.beta + t * a.heads + h);
+        }
+        cp_async_commit();
+    };
+    float* buf0 = sh;
+    float* buf1 = sh + (size_t)DCHUNK * per;
+    stage(0, buf0);
+    for (int c0 = 0, it = 0; c0 < n; c0 += DCHUNK, ++it) {
+        float* cur = (it & 1) ? buf1 : buf0;
+        cp_async_wait_all();
+        __syncthreads();                                  // chunk `it` has landed; everyone is done with the other buffer
+        if (c0 + DCHUNK < n) stage(c0 + DCHUNK, (it & 1) ? buf0 : buf1);
+        const int nc = min(DCHUNK, n - c0);
+        for (int tt = 0; tt < nc; ++tt) {
+            const float* q = cur + (size_t)tt * per;
+            const float* k = q + dim;
+            const float* g = k + dim;
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int d = 4 * i + part;
+                if (d < dim) { s[i] *= g[d]; dot = fmaf(s[i], k[d], dot); }
+            }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            const float u = live ? g[dim + vdim] * (g[dim + j] - dot) : 0.f;
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int d = 4 * i + part;
+                if (d < dim) { s[i] = fmaf(k[d], u, s[i]); o = fmaf(s[i], q[d], o); }
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (live && part == 0) a.o[(size_t)(row0 + c0 + tt) * ((size_t)a.heads * vdim) + (size_t)h * vdim + j] = o;
         }
     }
     if (live) {
 #pragma unroll
-        for (int d = 0; d < DMAX; ++d)
-            if (d < dim) S[(size_t)d * vdim + j] = s[d];
+        for (int i = 0; i < DPT; ++i) {
+            const int d = 4 * i + part;
+            if (d < dim) S[(size_t)d * vdim + j] = s[i];
+        }
     }
 }
 
@@ -633,13 +750,28 @@ int launch_delta(const DeltaArgs& a, const float* gate, const float* out_norm, f
         delta_tail_kernel<<<dim3((ch + 127) / 128, n_req), 128, 0, stream>>>(a, n_req);
         FT_CHECK_CUDA(cudaGetLastError());
     }
-    const int threads = (a.vdim + 31) / 32 * 32;
-    const size_t smem = (size_t)DCHUNK * (3 * a.dim + a.vdim + 1) * 4;
+    const int threads = (4 * a.vdim + 31) / 32 * 32;           // four lanes per state column
+    const size_t smem = (size_t)2 * DCHUNK * (3 * a.dim + a.vdim + 1) * 4;
     const dim3 grid(n_req, a.heads);
-    if (a.dim <= 32) delta_rule_kernel<32><<<grid, threads, smem, stream>>>(a);
-    else if (a.dim <= 64) delta_rule_kernel<64><<<grid, threads, smem, stream>>>(a);
-    else if (a.dim <= 128) delta_rule_kernel<128><<<grid, threads, smem, stream>>>(a);
-    else delta_rule_kernel<256><<<grid, threads, smem, stream>>>(a);
+#define FT_DELTA(DPT_)                                                                                          \
+    do {                                                                                                        \
+        if (threads <= 512) {                                                                                   \
+            if (smem > 48 * 1024)                                                                               \
+                FT_CHECK_CUDA(cudaFuncSetAttribute(delta_rule_kernel<DPT_, 512>,                                \
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
+            delta_rule_kernel<DPT_, 512><<<grid, threads, smem, stream>>>(a);                                   \
+        } else {                                                                                                \
+            if (smem > 48 * 1024)                                                                               \
+                FT_CHECK_CUDA(cudaFuncSetAttribute(delta_rule_kernel<DPT_, 1024>,                               \
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
+            delta_rule_kernel<DPT_, 1024><<<grid, threads, smem, stream>>>(a);                                  \
+        }                                                                                                       \
+    } while (0)
+    if (a.dim <= 32) FT_DELTA(8);
+    else if (a.dim <= 64) FT_DELTA(16);
+    else if (a.dim <= 128) FT_DELTA(32);
+    else FT_DELTA(64);
+#undef FT_DELTA
     FT_CHECK_CUDA(cudaGetLastError());
     const int n_pairs = T * a.heads;
     delta_out_kernel<<<(n_pairs + 3) / 4, 128, 0, stream>>>(a.o, gate, out_norm, a.vdim, eps, n_pairs);
