@@ -183,6 +183,11 @@ struct Layered {
     int *ids = nullptr, *seg = nullptr, *slot_token = nullptr, *slot_pos = nullptr;
     void *pl_hi = nullptr, *pl_lo = nullptr;      // bf16 planes of a projection's input [t_max][k_max]
     void *hn_hi = nullptr, *hn_lo = nullptr;      // bf16 planes of the normed layer input [t_max][width]
+    // experts on the tensor cores: planes of the gathered rows, fp32 gate/up results, planes of the activations, and the
+    // segment table on the host (the per-expert launches need the row counts)
+    void *mx_hi = nullptr, *mx_lo = nullptr, *ax_hi = nullptr, *ax_lo = nullptr;
+    float* gu = nullptr;
+    int* h_seg = nullptr;
     bool tensor = false;               // projections that tile run on the tensor cores (ft_layered_model.exact_f32 == 0)
     float* trail = nullptr;            // debug: residual stream after every layer [n_layers][t_max][width]
     bool trail_on = false;
@@ -542,7 +547,8 @@ static int forward(Engine* e, const Batch& b) {
 // A plain projection C[T][N] = A[T][K] W[N][K]^T.  With enough rows and shapes that tile, on the tensor cores: the fp32 input
 // as bf16 hi + lo planes (`hi` / `lo` if the producer already wrote them, else staged here), fp32 out.  Otherwise, and always
 // in the exact-fp32 form, the CUDA-core kernels.
-constexpr int kTensorMinRows = 17;
+constexpr int kTensorMinRows = 9;
+constexpr int kMoeTensorMinPairs = 256;      // (token, choice) pairs from which the experts run as per-expert tensor-core GEMMs
 static int dense(Engine* e, const float* A, const void* hi, const void* lo, const void* W, float* C, int T, int N, int K,
                  float softcap = 0.f) {
     Layered& L = *e->lay;
@@ -641,6 +647,37 @@ static int forward_layered(Engine* e, const Batch& b) {
             top = c.top;
             FT_TRY(launch_route(L.proj, ld, c.o_router, c.experts, c.top, c.groups, c.keep, L.ids, L.wts, L.seg,
                                 L.slot_token, L.slot_pos, T, st));
+            const int pairs = T * top;
+            const bool on_tensor = L.tensor && pairs >= kMoeTensorMinPairs && (2 * c.ff) % 128 == 0 && c.ff % 64 == 0 &&
+                                   W % 128 == 0;
+            if (on_tensor) {
+                // One tcgen05 GEMM per expert over its run of sorted rows.  The launches need the run lengths on the host:
+                // a copy of E + 1 integers and a wait, a few microseconds against the milliseconds of such a step.
+                FT_CHECK_CUDA(cudaMemcpyAsync(L.h_seg, L.seg, (size_t)(c.experts + 1) * 4, cudaMemcpyDeviceToHost, st));
+                FT_TRY(launch_gather_planes_rows(L.hn, L.slot_token, L.mx_hi, L.mx_lo, pairs, W, st));
+                FT_CHECK_CUDA(cudaStreamSynchronize(st));
+                auto off = [](const void* p, size_t elems) { return (const void*)((const uint8_t*)p + elems * 2); };
+                ft_gemm_epilogue ep = {};
+                ep.mode = FT_EPI_PARTIAL;
+                for (int x = 0; x < c.experts; ++x) {
+                    const int r0 = L.h_seg[x], nr = L.h_seg[x + 1] - r0;
+                    if (nr <= 0) continue;
+                    ep.out = L.gu + (size_t)r0 * 2 * c.ff;
+                    FT_TRY(ft_gemm_fused(off(c.w_gu, (size_t)x * 2 * c.ff * W), off(L.mx_hi, (size_t)r0 * W),
+                                         off(L.mx_lo, (size_t)r0 * W), 2 * c.ff, nr, W, 1, &ep, st));
+                    launched();
+                }
+                FT_TRY(launch_swiglu_planes(L.gu, L.ax_hi, L.ax_lo, (size_t)pairs * c.ff, st));
+                for (int x = 0; x < c.experts; ++x) {
+                    const int r0 = L.h_seg[x], nr = L.h_seg[x + 1] - r0;
+                    if (nr <= 0) continue;
+                    ep.out = L.eout + (size_t)r0 * W;
+                    FT_TRY(ft_gemm_fused(off(c.w_down, (size_t)x * W * c.ff), off(L.ax_hi, (size_t)r0 * c.ff),
+                                         off(L.ax_lo, (size_t)r0 * c.ff), W, nr, c.ff, 1, &ep, st));
+                    launched();
+                }
+                launched(4);
+            } else {
             LinearArgs gu;                  // gate and up of every (token, choice) pair, grouped by expert
             gu.A = L.hn; gu.a_rows = L.slot_token; gu.lda = W; gu.W = (const __nv_bfloat16*)c.w_gu;
             gu.w_stride = (long long)2 * c.ff * W; gu.ldw = W; gu.C = L.act; gu.ldc = c.ff; gu.seg = L.seg;
@@ -650,6 +687,7 @@ static int forward_layered(Engine* e, const Batch& b) {
             dn.A = L.act; dn.lda = c.ff; dn.W = (const __nv_bfloat16*)c.w_down; dn.w_stride = (long long)W * c.ff;
             dn.ldw = c.ff; dn.C = L.eout; dn.ldc = W; dn.seg = L.seg; dn.N = W; dn.K = c.ff; dn.P = c.experts;
             FT_TRY(launch_linear(dn, T * top, st));
+            }
             launched(4);
         }
         const float gain_next = l + 1 < M.n_layers ? L.layers[l + 1].d.norm_gain : M.final_norm_gain;
@@ -1236,6 +1274,11 @@ static int engine_init_layered(Engine* e) {
         FT_TRY(alloc(&L.pl_lo, std::max<size_t>(T, rows_last_min) * k_max * 2));
         FT_TRY(alloc(&L.hn_hi, T * W * 2));
         FT_TRY(alloc(&L.hn_lo, T * W * 2));
+        FT_TRY(alloc(&L.mx_hi, T * top_max * W * 2));
+        FT_TRY(alloc(&L.mx_lo, T * top_max * W * 2));
+        FT_TRY(alloc(&L.ax_hi, T * top_max * act_cols * 2));
+        FT_TRY(alloc(&L.ax_lo, T * top_max * act_cols * 2));
+        FT_TRY(alloc(&L.gu, T * top_max * act_cols * 2 * 4));
     }
     FT_TRY(alloc(&L.b1, T * buf * 4));
     FT_TRY(alloc(&L.b2, T * buf * 4));
@@ -1254,6 +1297,7 @@ static int engine_init_layered(Engine* e) {
         int e_max = 1;
         for (const LayeredLayer& ll : L.layers) e_max = std::max(e_max, ll.d.experts);
         FT_TRY(alloc(&L.seg, (size_t)(e_max + 1) * 4));
+        FT_CHECK_CUDA(cudaMallocHost(&L.h_seg, (size_t)(e_max + 1) * 4));
     }
     const size_t rows_last = std::max<size_t>(e->logit_rows, 256);
     e->rows_last = (int)rows_last;
@@ -1283,6 +1327,8 @@ static void engine_free(Engine* e) {
         cudaFree(L.b3); cudaFree(L.b4); cudaFree(L.beta); cudaFree(L.attn_part); cudaFree(L.mix); cudaFree(L.act); cudaFree(L.eout);
         cudaFree(L.wts); cudaFree(L.xlast); cudaFree(L.ids); cudaFree(L.seg); cudaFree(L.slot_token);
         cudaFree(L.slot_pos); cudaFree(L.trail); cudaFree(L.pl_hi); cudaFree(L.pl_lo); cudaFree(L.hn_hi); cudaFree(L.hn_lo);
+        cudaFree(L.mx_hi); cudaFree(L.mx_lo); cudaFree(L.ax_hi); cudaFree(L.ax_lo); cudaFree(L.gu);
+        if (L.h_seg) cudaFreeHost(L.h_seg);
         delete e->lay;
     }
     if (e->meta.h) cudaFreeHost(e->meta.h);

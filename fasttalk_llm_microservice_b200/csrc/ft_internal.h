@@ -114,6 +114,8 @@ int launch_embed_norm(const int* tokens, const void* embed, float* x, float* hn,
                       float gain, cudaStream_t stream);
 int launch_to_planes(const float* x, void* hi, void* lo, size_t n, cudaStream_t stream);
 int launch_softcap(float* x, size_t n, float cap, cudaStream_t stream);
+int launch_gather_planes_rows(const float* src, const int* idx, void* hi, void* lo, int n, int W, cudaStream_t stream);
+int launch_swiglu_planes(const float* gu, void* hi, void* lo, size_t n, cudaStream_t stream);
 int launch_combine_norm(float* x, float* hn, const float* proj, int ldp, int o_rg1, int o_rg2, const float* rg_bias,
                         const float* mix, const float* eout, const float* wt, const int* slot_pos, int top, int T, int W,
                         float eps, float gain, void* hi, void* lo, cudaStream_t stream);

@@ -149,87 +149,107 @@ __global__ void __launch_bounds__(LTHREADS) linear_tile_kernel(LinearArgs a) {
 }
 
 // ------------------------------------------------------------------ linear: few rows (decode)
-// One warp per output column (per pair of columns with the SwiGLU epilogue) and up to LROWS rows: the weights are read
-// once per block of LROWS rows, 16 bytes per lane per load; the rows come from L1 / L2.
-constexpr int LROWS = 16;
+// A CTA of 8 warps owns 32 output columns (16 column pairs with the SwiGLU epilogue) of one problem and walks its rows
+// LROWS at a time: a 512-wide slice of those rows is staged in shared memory once and reused by every column, each warp
+// streams the weights of its columns 16 bytes per lane per load, so the weights are read once per LROWS rows.
+constexpr int LROWS = 16, LKC = 512, LWARPS = 8;
 
-__global__ void __launch_bounds__(256) linear_rows_kernel(LinearArgs a) {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    const bool pair = a.epi == LIN_SWIGLU_PAIR;
-    const int cols = pair ? a.N / 2 : a.N;
+template <bool PAIR, bool VEC>
+__global__ void __launch_bounds__(LWARPS * 32) linear_rows_kernel(LinearArgs a) {
+    constexpr int CPW = PAIR ? 2 : 4;                 // output columns per warp
+    constexpr int WR = PAIR ? 2 * CPW : CPW;          // weight rows per warp
+    __shared__ __align__(16) float sA[LROWS][LKC];
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cols = PAIR ? a.N / 2 : a.N;
     const int p = blockIdx.y;
-    if (warp >= cols) return;
+    const int col0 = (blockIdx.x * LWARPS + wid) * CPW;
     int r0 = 0, r1 = a.M;
     if (a.seg) { r0 = a.seg[p]; r1 = a.seg[p + 1]; }
     if (r1 <= r0) return;
     const float* A = a.A + (size_t)p * a.a_col_stride;
     const __nv_bfloat16* W = a.W + (size_t)p * a.w_stride;
     float* C = a.C + (size_t)p * a.c_col_stride;
-    const int n = pair ? 2 * warp : warp;
-    const __nv_bfloat16* w0 = W + (size_t)n * a.ldw;
-    const __nv_bfloat16* w1 = w0 + a.ldw;
-    const bool vec = (a.K & 7) == 0 && (a.ldw & 7) == 0 && (a.lda & 3) == 0 && (a.a_col_stride & 3) == 0 &&
-                     (a.w_stride & 7) == 0 && ((uintptr_t)a.A & 15) == 0 && ((uintptr_t)a.W & 15) == 0;
+    const __nv_bfloat16* wrow[WR];
+    bool wok[WR];
+#pragma unroll
+    for (int c = 0; c < WR; ++c) {
+        const int n = PAIR ? 2 * col0 + c : col0 + c;
+        wok[c] = n < a.N;
+        wrow[c] = W + (size_t)(wok[c] ? n : 0) * a.ldw;
+    }
     for (int rb = r0; rb < r1; rb += LROWS) {
         const int nr = min(LROWS, r1 - rb);
-        const float* ar[LROWS];
+        float acc[WR][LROWS];
 #pragma unroll
-        for (int i = 0; i < LROWS; ++i) {
-            const int r = rb + (i < nr ? i : 0);
-            ar[i] = A + (size_t)(a.a_rows ? a.a_rows[r] : r) * a.lda;
-        }
-        float acc0[LROWS], acc1[LROWS];
+        for (int c = 0; c < WR; ++c)
 #pragma unroll
-        for (int i = 0; i < LROWS; ++i) acc0[i] = acc1[i] = 0.f;
-        if (vec) {
-            for (int k = lane * 8; k < a.K; k += 256) {
-                const uint4 t = __ldg(reinterpret_cast<const uint4*>(w0 + k));
-                const float wa[8] = {bf16_lo(t.x), bf16_hi(t.x), bf16_lo(t.y), bf16_hi(t.y),
-                                     bf16_lo(t.z), bf16_hi(t.z), bf16_lo(t.w), bf16_hi(t.w)};
-                float wb[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                if (pair) {
-                    const uint4 u = __ldg(reinterpret_cast<const uint4*>(w1 + k));
-                    wb[0] = bf16_lo(u.x); wb[1] = bf16_hi(u.x); wb[2] = bf16_lo(u.y); wb[3] = bf16_hi(u.y);
-                    wb[4] = bf16_lo(u.z); wb[5] = bf16_hi(u.z); wb[6] = bf16_lo(u.w); wb[7] = bf16_hi(u.w);
+            for (int i = 0; i < LROWS; ++i) acc[c][i] = 0.f;
+        for (int k0 = 0; k0 < a.K; k0 += LKC) {
+            const int kc = min(LKC, a.K - k0);
+            __syncthreads();
+            for (int i = wid; i < nr; i += LWARPS) {          // a warp per row
+                const int r = rb + i;
+                const float* src = A + (size_t)(a.a_rows ? a.a_rows[r] : r) * a.lda + k0;
+                if (VEC) {
+                    for (int k = lane * 4; k < kc; k += 128)
+                        *reinterpret_cast<float4*>(&sA[i][k]) = *reinterpret_cast<const float4*>(src + k);
+                } else {
+                    for (int k = lane; k < kc; k += 32) sA[i][k] = src[k];
                 }
+            }
+            __syncthreads();
+            if (VEC) {
+                for (int k = lane * 8; k < kc; k += 256) {
+                    float wv[WR][8];
 #pragma unroll
-                for (int i = 0; i < LROWS; ++i) {
-                    if (i < nr) {
-                        const float4 x0 = *reinterpret_cast<const float4*>(ar[i] + k);
-                        const float4 x1 = *reinterpret_cast<const float4*>(ar[i] + k + 4);
-                        const float xa[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                    for (int c = 0; c < WR; ++c) {
+                        uint4 t = make_uint4(0u, 0u, 0u, 0u);
+                        if (wok[c]) t = __ldg(reinterpret_cast<const uint4*>(wrow[c] + k0 + k));
+                        wv[c][0] = bf16_lo(t.x); wv[c][1] = bf16_hi(t.x); wv[c][2] = bf16_lo(t.y); wv[c][3] = bf16_hi(t.y);
+                        wv[c][4] = bf16_lo(t.z); wv[c][5] = bf16_hi(t.z); wv[c][6] = bf16_lo(t.w); wv[c][7] = bf16_hi(t.w);
+                    }
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) acc0[i] = fmaf(xa[e], wa[e], acc0[i]);
-                        if (pair) {
+                    for (int i = 0; i < LROWS; ++i) {
+                        if (i < nr) {
+                            const float4 x0 = *reinterpret_cast<const float4*>(&sA[i][k]);
+                            const float4 x1 = *reinterpret_cast<const float4*>(&sA[i][k + 4]);
+                            const float xa[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) acc1[i] = fmaf(xa[e], wb[e], acc1[i]);
+                            for (int c = 0; c < WR; ++c)
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) acc[c][i] = fmaf(xa[e], wv[c][e], acc[c][i]);
                         }
                     }
                 }
-            }
-        } else {
-            for (int k = lane; k < a.K; k += 32) {
-                const float wa = __bfloat162float(w0[k]);
-                const float wb = pair ? __bfloat162float(w1[k]) : 0.f;
+            } else {
+                for (int k = lane; k < kc; k += 32) {
+                    float wv[WR];
 #pragma unroll
-                for (int i = 0; i < LROWS; ++i)
-                    if (i < nr) {
-                        const float x = ar[i][k];
-                        acc0[i] = fmaf(x, wa, acc0[i]);
-                        acc1[i] = fmaf(x, wb, acc1[i]);
-                    }
+                    for (int c = 0; c < WR; ++c) wv[c] = wok[c] ? __bfloat162float(wrow[c][k0 + k]) : 0.f;
+#pragma unroll
+                    for (int i = 0; i < LROWS; ++i)
+                        if (i < nr) {
+                            const float x = sA[i][k];
+#pragma unroll
+                            for (int c = 0; c < WR; ++c) acc[c][i] = fmaf(x, wv[c], acc[c][i]);
+                        }
+                }
             }
         }
 #pragma unroll
-        for (int i = 0; i < LROWS; ++i) {
-            if (i >= nr) continue;               // uniform over the warp
-            const float s0 = warp_sum(acc0[i]);
-            const float s1 = pair ? warp_sum(acc1[i]) : 0.f;
-            if (lane == 0) {
-                float v = s0;
-                if (pair) v = s0 / (1.f + expf(-s0)) * s1;
-                else if (a.epi == LIN_SOFTCAP) v = a.cap * tanhf(v / a.cap);
-                C[(size_t)(rb + i) * a.ldc + warp] = v;
+        for (int c = 0; c < CPW; ++c) {
+#pragma unroll
+            for (int i = 0; i < LROWS; ++i) {
+                if (i >= nr) continue;               // uniform over the warp
+                float v;
+                if (PAIR) {
+                    const float g = warp_sum(acc[2 * c][i]), u = warp_sum(acc[2 * c + 1][i]);
+                    v = g / (1.f + expf(-g)) * u;
+                } else {
+                    v = warp_sum(acc[c][i]);
+                    if (a.epi == LIN_SOFTCAP) v = a.cap * tanhf(v / a.cap);
+                }
+                if (lane == 0 && col0 + c < cols) C[(size_t)(rb + i) * a.ldc + col0 + c] = v;
             }
         }
     }
@@ -242,9 +262,19 @@ int launch_linear(const LinearArgs& a, int rows_bound, cudaStream_t stream) {
     // few rows per problem: one warp per output column, the weights stream once
     const bool few = a.seg ? rows_bound <= 4 * LROWS : rows_bound <= 2 * LROWS;
     if (few) {
-        const int cols = a.epi == LIN_SWIGLU_PAIR ? a.N / 2 : a.N;
-        dim3 grid((cols + 7) / 8, a.P);
-        linear_rows_kernel<<<grid, 256, 0, stream>>>(a);
+        const bool pair = a.epi == LIN_SWIGLU_PAIR;
+        const int cols = pair ? a.N / 2 : a.N;
+        const int per_cta = LWARPS * (pair ? 2 : 4);
+        const bool v8 = (a.K & 7) == 0 && (a.ldw & 7) == 0 && (a.lda & 3) == 0 && (a.a_col_stride & 3) == 0 &&
+                        (a.w_stride & 7) == 0 && ((uintptr_t)a.A & 15) == 0 && ((uintptr_t)a.W & 15) == 0;
+        dim3 grid((cols + per_cta - 1) / per_cta, a.P);
+        if (pair) {
+            if (v8) linear_rows_kernel<true, true><<<grid, LWARPS * 32, 0, stream>>>(a);
+            else linear_rows_kernel<true, false><<<grid, LWARPS * 32, 0, stream>>>(a);
+        } else {
+            if (v8) linear_rows_kernel<false, true><<<grid, LWARPS * 32, 0, stream>>>(a);
+            else linear_rows_kernel<false, false><<<grid, LWARPS * 32, 0, stream>>>(a);
+        }
         FT_CHECK_CUDA(cudaGetLastError());
         return 0;
     }
@@ -277,6 +307,35 @@ __global__ void to_planes_kernel(const float* __restrict__ x, __nv_bfloat16* __r
 __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         x[i] = cap * tanhf(x[i] / cap);
+}
+
+// planes of the rows an index list names: out row i = planes(src[idx[i]])
+__global__ void gather_planes_kernel2(const float* __restrict__ src, const int* __restrict__ idx, __nv_bfloat16* __restrict__ hi,
+                                      __nv_bfloat16* __restrict__ lo, int W) {
+    const size_t i = blockIdx.x;
+    const float* r = src + (size_t)idx[i] * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) store_planes(hi, lo, i * W + c, r[c]);
+}
+
+// gu [rows][2 ff] with columns (2j, 2j+1) = (gate_j, up_j)  ->  planes of silu(gate) * up, [rows][ff]
+__global__ void swiglu_planes_kernel(const float* __restrict__ gu, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+                                     size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float2 v = reinterpret_cast<const float2*>(gu)[i];
+        store_planes(hi, lo, i, v.x / (1.f + expf(-v.x)) * v.y);
+    }
+}
+
+int launch_gather_planes_rows(const float* src, const int* idx, void* hi, void* lo, int n, int W, cudaStream_t stream) {
+    gather_planes_kernel2<<<n, 256, 0, stream>>>(src, idx, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, W);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+int launch_swiglu_planes(const float* gu, void* hi, void* lo, size_t n, cudaStream_t stream) {
+    const int blocks = (int)std::min<size_t>((n + 255) / 256, 148 * 16);
+    swiglu_planes_kernel<<<blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, n);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
 }
 
 int launch_to_planes(const float* x, void* hi, void* lo, size_t n, cudaStream_t stream) {
