@@ -682,13 +682,13 @@ __global__ void delta_tail_kernel(DeltaArgs a, int n_req) {
     for (int i = 0; i < keep; ++i) tail[i] = v[i];
 }
 
-// The recurrence, one CTA per (request, head).  Per token
+// The recurrence, one CTA per (request, head, block of DCOLS state columns).  Per token
 //   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 // is local to a column of the state S [dim][vdim].  Four neighbouring lanes share a column, each holding every fourth key
 // channel of it in registers (DPT values), so the two sums over key channels are a short chain plus two shuffles.
 // q, k, g, v, beta of DCHUNK tokens at a time are copied into shared memory asynchronously (cp.async), one chunk ahead
 // of the one being computed.
-constexpr int DCHUNK = 8;
+constexpr int DCHUNK = 8, DCOLS = 32;
 __device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
 }
@@ -700,7 +700,7 @@ __global__ void __launch_bounds__(MAXT)
 delta_rule_kernel(DeltaArgs a) {
     extern __shared__ float sh[];
     const int req = blockIdx.x, h = blockIdx.y;
-    const int j = threadIdx.x >> 2, part = threadIdx.x & 3;      // column, and which quarter of the key channels
+    const int j = blockIdx.z * DCOLS + (threadIdx.x >> 2), part = threadIdx.x & 3;      // column, and which quarter of the key channels
     const int kh = h / (a.heads / a.kvh);
     const int row0 = a.req_start[req], n = a.req_start[req + 1] - row0;
     const int dim = a.dim, vdim = a.vdim;
@@ -809,9 +809,9 @@ int launch_delta(const DeltaArgs& a, const float* gate, const float* out_norm, f
         delta_tail_kernel<<<dim3((ch + 127) / 128, n_req), 128, 0, stream>>>(a, n_req);
         FT_CHECK_CUDA(cudaGetLastError());
     }
-    const int threads = (4 * a.vdim + 31) / 32 * 32;           // four lanes per state column
+    const int threads = (4 * std::min(a.vdim, DCOLS) + 31) / 32 * 32;      // four lanes per state column, whole warps
     const size_t smem = (size_t)2 * DCHUNK * (3 * a.dim + a.vdim + 1) * 4;
-    const dim3 grid(n_req, a.heads);
+    const dim3 grid(n_req, a.heads, (a.vdim + DCOLS - 1) / DCOLS);
 #define FT_DELTA(DPT_)                                                                                          \
     do {                                                                                                        \
         if (threads <= 512) {                                                                                   \
