@@ -278,8 +278,8 @@ def _env_int(name, default):
 
 
 def build_runner(model: str) -> EngineRunner:
-    """Create the engine for `model` on GPU $FASTTALK_GPU: weights from $FASTTALK_CHECKPOINT (a
-    Hugging Face Llama directory) or $FASTTALK_WEIGHTS (stacked layout), else random-init."""
+    """Create the engine for `model` on GPU $FASTTALK_GPU: weights from $FASTTALK_CHECKPOINT (a Hugging Face Llama
+    directory or a layered model's directory, registry.py) or $FASTTALK_WEIGHTS (stacked layout), else random-init."""
     import torch
     from .engine import Engine, EngineLimits
     from .model_spec import get_spec
@@ -291,9 +291,9 @@ def build_runner(model: str) -> EngineRunner:
     torch.cuda.set_device(dev)
     ckpt = os.environ.get("FASTTALK_CHECKPOINT")
     tok_path = None
-    if ckpt:                            # a Hugging Face Llama directory: config.json + *.safetensors (+ tokenizer.json)
-        from .checkpoint import load_hf_checkpoint
-        spec, w = load_hf_checkpoint(ckpt, device=f"cuda:{dev}", name=model)
+    if ckpt:                            # a checkpoint directory: config.json + *.safetensors (+ tokenizer.json); its
+        from .registry import load_model    # config.json says which family it is (Hugging Face Llama, or a layered model)
+        spec, w = load_model(ckpt, device=f"cuda:{dev}", name=model)
         if os.path.exists(os.path.join(ckpt, "tokenizer.json")):
             tok_path = os.path.join(ckpt, "tokenizer.json")
     else:

@@ -45,6 +45,14 @@ def ollama_routes(handler, served: str, keys) -> List[Route]:
         eng = handler.runner.engine
         spec = getattr(eng, "spec", None)
         info = {"general.architecture": "llama"}
+        if spec is not None and hasattr(spec, "architecture"):      # a layered model (layered.py) describes itself
+            arch = str(spec.architecture).lower()
+            info = {"general.architecture": arch, f"{arch}.block_count": len(spec.layers),
+                    f"{arch}.embedding_length": spec.width,
+                    f"{arch}.context_length": getattr(getattr(eng, "limits", None), "max_context", None)}
+            return {"modelfile": f"FROM {served}", "parameters": "", "template": "llama3",
+                    "details": {"family": arch, "format": "fasttalk_b200", "quantization_level": "BF16"},
+                    "model_info": info}
         if spec is not None:
             info.update({"llama.block_count": spec.layers, "llama.embedding_length": spec.hidden,
                          "llama.attention.head_count": spec.n_q_heads, "llama.attention.head_count_kv": spec.n_kv_heads,

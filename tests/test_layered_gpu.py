@@ -377,3 +377,30 @@ def test_projections_on_tensor_cores_and_in_exact_fp32(exact):
         assert rel(got, ref) < (TOL if exact else 3e-4)
     finally:
         eng.close()
+
+
+def test_served_through_the_handler(tmp_path, monkeypatch):
+    """A layered checkpoint behind the serving path: FASTTALK_CHECKPOINT -> registry -> engine -> NativeHandler streams text."""
+    from fasttalk_llm_microservice_b200.handler import NativeHandler
+    from fasttalk_llm_microservice_b200.layered import save_checkpoint
+    spec, w = make([delta(**moe()), latent()], width=64, vocab=600, seed=41)
+    save_checkpoint(spec, w, str(tmp_path / "ckpt"))
+    monkeypatch.setenv("FASTTALK_CHECKPOINT", str(tmp_path / "ckpt"))
+    monkeypatch.setenv("FASTTALK_ALLOW_BYTE_TOKENIZER", "1")
+    monkeypatch.setenv("FASTTALK_MAX_SESSIONS", "4")
+    monkeypatch.setenv("FASTTALK_MAX_CONTEXT", "512")
+    monkeypatch.setenv("FASTTALK_MAX_BATCHED_TOKENS", "256")
+    from fasttalk_llm_microservice_b200.handler import build_runner
+    runner = build_runner("gitozen-test")
+    h = NativeHandler(model="gitozen-test", runner=runner)
+    try:
+        assert h.check_connection()
+        chunks = list(h.generate_stream([{"role": "user", "content": "hello there"}], temperature=0.0, max_tokens=12,
+                                        request_id="conv-1"))
+        assert 1 <= len(chunks) <= 12
+        st = h.runner.engine.stats()
+        assert st["prefill_tokens"] > 0 and st["decode_tokens"] > 0
+    finally:
+        h.close()
+        runner.shutdown()
+        runner.engine.close()
