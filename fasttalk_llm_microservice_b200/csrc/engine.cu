@@ -174,6 +174,7 @@ struct Layered {
     ft_layered_model m;
     std::vector<LayeredLayer> layers;
     float* lat_cache = nullptr;
+    void* lat_cache16 = nullptr;       // serving form: bf16 copy of the latents, same places (tensor-core attention)
     float* state = nullptr;
     size_t slot_stride = 0;            // floats per state slot
     int n_stateful = 0;                // layers whose mixer carries state from token to token
@@ -601,7 +602,8 @@ static int forward_layered(Engine* e, const Batch& b) {
         const float* mixed = nullptr;      // [T][heads * vdim], input of the output projection
         if (c.mixer == FT_MIXER_LATENT_ATTENTION) {
             float* cache = L.lat_cache + ll.cache_off;
-            FT_TRY(launch_latent_write(L.proj, ld, c.o_dkv, c.dkv_norm, cache, d + m.o_pos, d + m.o_rows, d + m.o_pt,
+            void* cache16 = L.lat_cache16 ? (uint8_t*)L.lat_cache16 + ll.cache_off * 2 : nullptr;
+            FT_TRY(launch_latent_write(L.proj, ld, c.o_dkv, c.dkv_norm, cache, cache16, d + m.o_pos, d + m.o_rows, d + m.o_pt,
                                        e->max_pages, c.kv_rank, M.eps, T, st));
             LinearArgs a;                   // queries into latent space, head by head: qlat_h = W_uk_h^T q_h
             a.A = L.proj + c.o_q; a.lda = ld; a.a_col_stride = c.dim;
@@ -609,7 +611,7 @@ static int forward_layered(Engine* e, const Batch& b) {
             a.C = L.b1; a.ldc = c.heads * c.kv_rank; a.c_col_stride = c.kv_rank;
             a.M = T; a.N = c.kv_rank; a.K = c.dim; a.P = c.heads;
             FT_TRY(launch_linear(a, T, st));
-            FT_TRY(launch_latent_attn(L.b1, cache, L.proj, ld, c.o_gate, L.b2, L.attn_part, d + m.o_pos, d + m.o_rows, d + m.o_pt,
+            FT_TRY(launch_latent_attn(L.b1, cache, cache16, L.proj, ld, c.o_gate, L.b2, L.attn_part, d + m.o_pos, d + m.o_rows, d + m.o_pt,
                                       e->max_pages, c.heads, c.kv_rank, c.scale, T, st));
             LinearArgs v;                   // values out of latent space: o_h = W_uv_h (sum_j p_j c_j)
             v.A = L.b2; v.lda = c.heads * c.kv_rank; v.a_col_stride = c.kv_rank;
@@ -1264,6 +1266,7 @@ static int engine_init_layered(Engine* e) {
         return 0;
     };
     FT_TRY(alloc(&L.lat_cache, cache_floats * 4));
+    if (M.exact_f32 == 0) FT_TRY(alloc(&L.lat_cache16, cache_floats * 2));
     FT_TRY(alloc(&L.state, L.slot_stride * (size_t)c.max_sessions * 4));
     FT_TRY(alloc(&e->resid, T * W * 4));
     FT_TRY(alloc(&L.hn, T * W * 4));
@@ -1323,7 +1326,7 @@ static void engine_free(Engine* e) {
     cudaFree(e->x16_xn); cudaFree(e->x16_attn); cudaFree(e->x16_act);
     if (e->lay) {
         Layered& L = *e->lay;
-        cudaFree(L.lat_cache); cudaFree(L.state); cudaFree(L.hn); cudaFree(L.proj); cudaFree(L.b1); cudaFree(L.b2);
+        cudaFree(L.lat_cache); cudaFree(L.lat_cache16); cudaFree(L.state); cudaFree(L.hn); cudaFree(L.proj); cudaFree(L.b1); cudaFree(L.b2);
         cudaFree(L.b3); cudaFree(L.b4); cudaFree(L.beta); cudaFree(L.attn_part); cudaFree(L.mix); cudaFree(L.act); cudaFree(L.eout);
         cudaFree(L.wts); cudaFree(L.xlast); cudaFree(L.ids); cudaFree(L.seg); cudaFree(L.slot_token);
         cudaFree(L.slot_pos); cudaFree(L.trail); cudaFree(L.pl_hi); cudaFree(L.pl_lo); cudaFree(L.hn_hi); cudaFree(L.hn_lo);

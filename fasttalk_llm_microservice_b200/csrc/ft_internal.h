@@ -120,16 +120,20 @@ int launch_combine_norm(float* x, float* hn, const float* proj, int ldp, int o_r
                         const float* mix, const float* eout, const float* wt, const int* slot_pos, int top, int T, int W,
                         float eps, float gain, void* hi, void* lo, cudaStream_t stream);
 int launch_gather_rows(const float* src, const int* idx, float* dst, int n, int W, cudaStream_t stream);
-int launch_latent_write(const float* proj, int ldp, int o_dkv, const float* w, float* cache, const int* positions,
+// cache16 (may be null): a bf16 copy of the latents, what the tensor-core attention reads
+int launch_latent_write(const float* proj, int ldp, int o_dkv, const float* w, float* cache, void* cache16, const int* positions,
                         const int* seq_rows, const int* page_table, int max_pages, int rank, float eps, int T,
                         cudaStream_t stream);
 // With fewer than kLatentSplitPairs (token, head) pairs in a step the keys of each are cut into up to kLatentMaxSplits
 // shares that run side by side; `part` then holds pairs x shares x (kv_rank + 2) floats (null: never split).
 constexpr int kLatentSplitPairs = 2048, kLatentMaxSplits = 8;
 int latent_attn_splits(int T, int H);
-int launch_latent_attn(const float* qlat, const float* cache, const float* proj, int ldp, int o_gate, float* out, float* part,
-                       const int* positions, const int* seq_rows, const int* page_table, int max_pages, int H, int rank,
-                       float scale, int T, cudaStream_t stream);
+// With cache16 and a latent size the tensor-core kernel is built for (latent_attn_mma_ok) the attention runs on mma.sync
+// from bf16 operands; otherwise on the CUDA cores in fp32.
+bool latent_attn_mma_ok(int rank);
+int launch_latent_attn(const float* qlat, const float* cache, const void* cache16, const float* proj, int ldp, int o_gate,
+                       float* out, float* part, const int* positions, const int* seq_rows, const int* page_table, int max_pages,
+                       int H, int rank, float scale, int T, cudaStream_t stream);
 struct DeltaArgs {
     const float* proj = nullptr;      // [T][ldp]: raw q | k | v at column o_q, beta logits at o_beta
     int ldp = 0, o_q = 0, o_beta = 0;

@@ -41,6 +41,13 @@ __device__ __forceinline__ float block_sum(float v, float* red) {      // red: >
     return red[32];
 }
 
+// asynchronous global -> shared copies (the staging of the delta rule and of the tensor-core attention)
+__device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // ------------------------------------------------------------------ linear: tile kernel
 constexpr int LBM = 64, LBN = 64, LBK = 16, LTHREADS = 256;
 
@@ -442,7 +449,7 @@ int launch_gather_rows(const float* src, const int* idx, float* dst, int n, int 
 // of the layer's cache [page][64][rank] fp32.
 __global__ void __launch_bounds__(128)
 latent_write_kernel(const float* __restrict__ proj, int ldp, int o_dkv, const float* __restrict__ w, float* __restrict__ cache,
-                    const int* __restrict__ positions, const int* __restrict__ seq_rows, const int* __restrict__ page_table,
+                    __nv_bfloat16* __restrict__ cache16, const int* __restrict__ positions, const int* __restrict__ seq_rows, const int* __restrict__ page_table,
                     int max_pages, int rank, float eps) {
     __shared__ float red[33];
     const int t = blockIdx.x;
@@ -453,8 +460,12 @@ latent_write_kernel(const float* __restrict__ proj, int ldp, int o_dkv, const fl
     const float r = 1.f / sqrtf(ss / (float)rank + eps);
     const int pos = positions[t];
     const int page = page_table[(size_t)seq_rows[t] * max_pages + pos / kKvTile];
-    float* dst = cache + ((size_t)page * kKvTile + pos % kKvTile) * rank;
-    for (int c = threadIdx.x; c < rank; c += blockDim.x) dst[c] = raw[c] * r * w[c];
+    const size_t at = ((size_t)page * kKvTile + pos % kKvTile) * rank;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        const float v = raw[c] * r * w[c];
+        cache[at + c] = v;
+        if (cache16) cache16[at + c] = __float2bfloat16_rn(v);      // the tensor-core attention's copy
+    }
 }
 
 // One warp per (token, head, key range): the query in latent space stays in registers (NR values per lane), keys = values =
@@ -577,12 +588,182 @@ latent_merge_kernel(const float* __restrict__ part, const float* __restrict__ pr
     }
 }
 
-int launch_latent_write(const float* proj, int ldp, int o_dkv, const float* w, float* cache, const int* positions,
+int launch_latent_write(const float* proj, int ldp, int o_dkv, const float* w, float* cache, void* cache16, const int* positions,
                         const int* seq_rows, const int* page_table, int max_pages, int rank, float eps, int T,
                         cudaStream_t stream) {
-    latent_write_kernel<<<T, 128, 0, stream>>>(proj, ldp, o_dkv, w, cache, positions, seq_rows, page_table, max_pages, rank, eps);
+    latent_write_kernel<<<T, 128, 0, stream>>>(proj, ldp, o_dkv, w, cache, (__nv_bfloat16*)cache16, positions, seq_rows, page_table,
+                                               max_pages, rank, eps);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
+}
+
+// The serving form of the same attention on the tensor cores (mma.sync m16n8k16, bf16 operands, fp32 accumulation and
+// softmax): one CTA per (token, key share, group of 16 heads).  The 16 heads are the M rows of every product, so all rows
+// of a tile see the same keys and one mask.  Each of the four warps takes every fourth 16-key tile of the share: the tile
+// (16 latents from the bf16 copy of the cache) is copied into the warp's own double buffer with cp.async one tile ahead,
+// S = Q C^T (ldmatrix fragments of Q and of the tile), online softmax in registers, O += P C with the SAME tile read
+// through ldmatrix.trans — keys and values are one array.  The warps' (max, sum, O) are merged through shared memory.
+// rank = 32 * RK <= 256 (O is rank / 8 accumulator tiles per thread).
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+template <int RK>
+__global__ void __launch_bounds__(128)
+latent_attn_mma_kernel(const float* __restrict__ qlat, const __nv_bfloat16* __restrict__ cache16, const float* __restrict__ proj,
+                       int ldp, int o_gate, float* __restrict__ out, float* __restrict__ part, const int* __restrict__ positions,
+                       const int* __restrict__ seq_rows, const int* __restrict__ page_table, int max_pages, int H, float scale,
+                       int n_split) {
+    constexpr int RANK = 32 * RK, RS = RANK * 2 + 16;      // row stride in bytes: 16 bytes of padding keep ldmatrix conflict-free
+    constexpr int TILE = 16 * RS;
+    extern __shared__ __align__(16) uint8_t lat_smem[];
+    uint8_t* Qs = lat_smem;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* kbuf = lat_smem + TILE + (size_t)warp * 2 * TILE;
+    const int t = blockIdx.x, split = blockIdx.y, h0 = blockIdx.z * 16;
+    for (int idx = threadIdx.x; idx < 16 * RANK; idx += 128) {
+        const int r = idx / RANK, c = idx % RANK;
+        const float v = h0 + r < H ? qlat[((size_t)t * H + h0 + r) * RANK + c] * scale : 0.f;
+        *reinterpret_cast<__nv_bfloat16*>(Qs + r * RS + c * 2) = __float2bfloat16_rn(v);
+    }
+    __syncthreads();
+    const int n_keys = positions[t] + 1;
+    int j_lo = 0, j_hi = n_keys;
+    if (n_split > 1) {
+        const int share = ((n_keys + n_split - 1) / n_split + kKvTile - 1) / kKvTile * kKvTile;
+        j_lo = min(split * share, n_keys);
+        j_hi = min(j_lo + share, n_keys);
+    }
+    const int* pt = page_table + (size_t)seq_rows[t] * max_pages;
+    const int n_tiles = (j_hi - j_lo + 15) / 16;
+    auto stage = [&](int tile, int buf) {
+        const int key0 = j_lo + tile * 16;
+        uint8_t* dst = kbuf + buf * TILE;
+        for (int i = lane; i < 16 * 4 * RK; i += 32) {          // 16 rows of 4 * RK 16-byte pieces
+            const int r = i / (4 * RK), ch = i % (4 * RK);
+            const int j = min(key0 + r, j_hi - 1);
+            cp_async16(dst + r * RS + ch * 16, cache16 + ((size_t)pt[j / kKvTile] * kKvTile + j % kKvTile) * RANK + ch * 8);
+        }
+        cp_async_commit();
+    };
+    float o[4 * RK][4];
+#pragma unroll
+    for (int nt = 0; nt < 4 * RK; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;      // rows g and g + 8
+    const int g = lane >> 2, tq = lane & 3;
+    const uint32_t q_addr = smem_u32(Qs) + ((lane & 7) + ((lane >> 3) & 1) * 8) * RS + (lane >> 4) * 16;
+    if (warp < n_tiles) stage(warp, 0);
+    for (int tile = warp, it = 0; tile < n_tiles; tile += 4, ++it) {
+        const int cur = it & 1;
+        if (tile + 4 < n_tiles) { stage(tile + 4, cur ^ 1); cp_async_wait_1(); }
+        else cp_async_wait_all();
+        __syncwarp();
+        const uint32_t kb = smem_u32(kbuf + cur * TILE);
+        float sc[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+        for (int kp = 0; kp < RK; ++kp) {                        // 32 latent channels per round
+            uint32_t a0[4], a1[4];
+            ldmatrix_x4(q_addr + (kp * 4) * 16, a0[0], a0[1], a0[2], a0[3]);
+            ldmatrix_x4(q_addr + (kp * 4 + 2) * 16, a1[0], a1[1], a1[2], a1[3]);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(kb + (8 * j + (lane & 7)) * RS + (kp * 4 + (lane >> 3)) * 16, b0, b1, b2, b3);
+                mma_bf16_16816(sc[j], a0[0], a0[1], a0[2], a0[3], b0, b1);
+                mma_bf16_16816(sc[j], a1[0], a1[1], a1[2], a1[3], b2, b3);
+            }
+        }
+        const int key0 = j_lo + tile * 16 + 2 * tq;
+        float ta = -INFINITY, tb = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                if (key0 + 8 * j + e >= j_hi) sc[j][e] = sc[j][2 + e] = -INFINITY;
+                ta = fmaxf(ta, sc[j][e]);
+                tb = fmaxf(tb, sc[j][2 + e]);
+            }
+        ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 1));
+        ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 2));
+        tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 1));
+        tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 2));
+        const float na = fmaxf(m_a, ta), nb = fmaxf(m_b, tb);      // finite: the tile's first key is never masked
+        const float alpha_a = expf(m_a - na), alpha_b = expf(m_b - nb);
+        float sa = 0.f, sb = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                sc[j][e] = expf(sc[j][e] - na);
+                sc[j][2 + e] = expf(sc[j][2 + e] - nb);
+                sa += sc[j][e];
+                sb += sc[j][2 + e];
+            }
+        l_a = l_a * alpha_a + sa;
+        l_b = l_b * alpha_b + sb;
+        m_a = na;
+        m_b = nb;
+        const uint32_t pa0 = pack_bf16(sc[0][0], sc[0][1]), pa1 = pack_bf16(sc[0][2], sc[0][3]);
+        const uint32_t pa2 = pack_bf16(sc[1][0], sc[1][1]), pa3 = pack_bf16(sc[1][2], sc[1][3]);
+        const int vrow = ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+        for (int np = 0; np < 2 * RK; ++np) {                    // 16 latent channels per round
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(kb + vrow * RS + (2 * np + (lane >> 4)) * 16, b0, b1, b2, b3);
+            o[2 * np][0] *= alpha_a; o[2 * np][1] *= alpha_a; o[2 * np][2] *= alpha_b; o[2 * np][3] *= alpha_b;
+            o[2 * np + 1][0] *= alpha_a; o[2 * np + 1][1] *= alpha_a; o[2 * np + 1][2] *= alpha_b; o[2 * np + 1][3] *= alpha_b;
+            mma_bf16_16816(o[2 * np], pa0, pa1, pa2, pa3, b0, b1);
+            mma_bf16_16816(o[2 * np + 1], pa0, pa1, pa2, pa3, b2, b3);
+        }
+        __syncwarp();
+    }
+    // the warp's record in its own (now idle) buffer: 16 rows of rank results, then max and sum
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    constexpr int REC = RANK + 2;
+    float* rec = reinterpret_cast<float*>(kbuf);
+#pragma unroll
+    for (int nt = 0; nt < 4 * RK; ++nt) {
+        rec[g * REC + nt * 8 + 2 * tq] = o[nt][0];
+        rec[g * REC + nt * 8 + 2 * tq + 1] = o[nt][1];
+        rec[(g + 8) * REC + nt * 8 + 2 * tq] = o[nt][2];
+        rec[(g + 8) * REC + nt * 8 + 2 * tq + 1] = o[nt][3];
+    }
+    if (tq == 0) {
+        rec[g * REC + RANK] = m_a; rec[g * REC + RANK + 1] = l_a;
+        rec[(g + 8) * REC + RANK] = m_b; rec[(g + 8) * REC + RANK + 1] = l_b;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * RANK; idx += 128) {
+        const int r = idx / RANK, c = idx % RANK;
+        if (h0 + r >= H) continue;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, reinterpret_cast<const float*>(lat_smem + TILE + (size_t)w * 2 * TILE)[r * REC + RANK]);
+        float l = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* rw = reinterpret_cast<const float*>(lat_smem + TILE + (size_t)w * 2 * TILE) + r * REC;
+            if (rw[RANK] > -INFINITY) {
+                const float f = expf(rw[RANK] - m);
+                l = fmaf(rw[RANK + 1], f, l);
+                a = fmaf(rw[c], f, a);
+            }
+        }
+        const size_t pair = (size_t)t * H + h0 + r;
+        if (n_split > 1) {
+            float* p = part + (pair * n_split + split) * REC;
+            p[2 + c] = a;
+            if (c == 0) { p[0] = m; p[1] = l; }
+        } else {
+            out[pair * RANK + c] = a / l * sigmoid_exact(proj[(size_t)t * ldp + o_gate + h0 + r]);
+        }
+    }
 }
 
 int latent_attn_splits(int T, int H) {
@@ -591,11 +772,41 @@ int latent_attn_splits(int T, int H) {
     return std::max(1, std::min(kLatentMaxSplits, kLatentSplitPairs / std::max(pairs, 1)));
 }
 
-int launch_latent_attn(const float* qlat, const float* cache, const float* proj, int ldp, int o_gate, float* out, float* part,
-                       const int* positions, const int* seq_rows, const int* page_table, int max_pages, int H, int rank,
-                       float scale, int T, cudaStream_t stream) {
+bool latent_attn_mma_ok(int rank) { return rank % 32 == 0 && rank >= 32 && rank <= 256; }
+
+int launch_latent_attn(const float* qlat, const float* cache, const void* cache16, const float* proj, int ldp, int o_gate,
+                       float* out, float* part, const int* positions, const int* seq_rows, const int* page_table, int max_pages,
+                       int H, int rank, float scale, int T, cudaStream_t stream) {
     const int n_pairs = T * H;
     const int n_split = part ? latent_attn_splits(T, H) : 1;
+    if (cache16 && latent_attn_mma_ok(rank)) {
+        const dim3 grid(T, n_split, (H + 15) / 16);
+        const size_t smem = (size_t)9 * 16 * (rank * 2 + 16);
+#define FT_LATM(RK_)                                                                                                        \
+    case RK_: {                                                                                                             \
+        static PerDeviceFlag attr;                                                                                          \
+        if (!attr.done()) {                                                                                                 \
+            FT_CHECK_CUDA(cudaFuncSetAttribute(latent_attn_mma_kernel<RK_>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                               9 * 16 * (RK_ * 64 + 16)));                                                  \
+            attr.mark();                                                                                                    \
+        }                                                                                                                   \
+        latent_attn_mma_kernel<RK_><<<grid, 128, smem, stream>>>(qlat, (const __nv_bfloat16*)cache16, proj, ldp, o_gate, out, \
+                                                                 part, positions, seq_rows, page_table, max_pages, H, scale, \
+                                                                 n_split);                                                  \
+        break;                                                                                                              \
+    }
+        switch (rank / 32) {
+            FT_LATM(1) FT_LATM(2) FT_LATM(3) FT_LATM(4) FT_LATM(5) FT_LATM(6) FT_LATM(7) FT_LATM(8)
+            default: break;
+        }
+#undef FT_LATM
+        FT_CHECK_CUDA(cudaGetLastError());
+        if (n_split > 1) {
+            latent_merge_kernel<<<(n_pairs + 3) / 4, 128, 0, stream>>>(part, proj, ldp, o_gate, out, H, rank, n_pairs, n_split);
+            FT_CHECK_CUDA(cudaGetLastError());
+        }
+        return 0;
+    }
     const dim3 grid((n_pairs + 3) / 4, n_split);
 #define FT_LAT(NR_, KB_)                                                                                                   \
     latent_attn_kernel<NR_, KB_><<<grid, 128, 0, stream>>>(qlat, cache, proj, ldp, o_gate, out, part, positions, seq_rows, \
@@ -689,11 +900,6 @@ __global__ void delta_tail_kernel(DeltaArgs a, int n_req) {
 // q, k, g, v, beta of DCHUNK tokens at a time are copied into shared memory asynchronously (cp.async), one chunk ahead
 // of the one being computed.
 constexpr int DCHUNK = 8, DCOLS = 32;
-__device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 template <int DPT, int MAXT>
 __global__ void __launch_bounds__(MAXT)

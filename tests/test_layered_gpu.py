@@ -404,3 +404,23 @@ def test_served_through_the_handler(tmp_path, monkeypatch):
         h.close()
         runner.shutdown()
         runner.engine.close()
+
+
+@pytest.mark.parametrize("sharp", [1.0, 16.0], ids=["plain", "sharp"])
+def test_latent_attention_on_tensor_cores(sharp):
+    """Latent sizes that are multiples of 32 take the mma.sync kernel in the serving form (bf16 queries, latents and softmax
+    weights, fp32 sums): 3 heads (one partly filled group of 16), 20 heads (two groups), prompts over several pages, single
+    tokens with key shares.  bf16 operands bound the agreement with the fp32 restatement; the exact engine stays at 1e-4.
+    With sharpened queries a lost or misplaced key would show far above either bound."""
+    layers = [latent(heads=3, dim=16, vdim=24, kv_rank=64, scale=0.3),
+              latent(heads=20, dim=8, vdim=8, kv_rank=32, scale=0.4, **moe(ff=24, experts=4, top=2, groups=2, keep=1))]
+    spec, w = make(layers, width=64, vocab=96, seed=43, tweak=sharpen(sharp))
+    toks = tokens_of(spec, 330, 44)
+    ref = oracle_logits(spec, w, toks)
+    for exact, tol in ((False, 2e-2), (True, TOL)):
+        eng = engine(spec, w, exact_f32=exact)
+        try:
+            got = feed_cut(eng, "a", toks, [190, 1, 1, 62, 1, 1, 1, 5, 1])
+            assert rel(got, ref) < tol, ("exact" if exact else "tensor cores")
+        finally:
+            eng.close()
