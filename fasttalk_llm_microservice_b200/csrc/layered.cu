@@ -895,18 +895,26 @@ __global__ void delta_tail_kernel(DeltaArgs a, int n_req) {
 
 // The recurrence, one CTA per (request, head, block of DCOLS state columns).  Per token
 //   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
-// is local to a column of the state S [dim][vdim].  Four neighbouring lanes share a column, each holding every fourth key
-// channel of it in registers (DPT values), so the two sums over key channels are a short chain plus two shuffles.
+// is local to a column of the state S [dim][vdim].  Four neighbouring lanes share a column, each holding a run of DPT key
+// channels of it in registers, so the two sums over key channels are two short chains plus two shuffles.
 // q, k, g, v, beta of DCHUNK tokens at a time are copied into shared memory asynchronously (cp.async), one chunk ahead
 // of the one being computed.
 constexpr int DCHUNK = 8, DCOLS = 32;
 
-template <int DPT, int MAXT>
+// Shared-memory layout of one staged token: q, k, g each as four runs of DPT channels (one per lane of a column's quad)
+// with four floats of padding between runs, so that the quad's 16-byte reads fall into different banks; then v, then beta.
+template <int DPT>
+__host__ __device__ constexpr int delta_run() { return DPT + 4; }
+__host__ __device__ inline int delta_token_floats(int dpt, int vdim) { return (12 * (dpt + 4) + vdim + 1 + 3) & ~3; }
+
+// FULL: dim == 4 * DPT, every channel test is true at compile time (the tests otherwise compile to branches in the token loop).
+template <int DPT, int MAXT, bool FULL>
 __global__ void __launch_bounds__(MAXT)
 delta_rule_kernel(DeltaArgs a) {
-    extern __shared__ float sh[];
+    extern __shared__ __align__(16) float sh[];
+    constexpr int RUN = delta_run<DPT>();
     const int req = blockIdx.x, h = blockIdx.y;
-    const int j = blockIdx.z * DCOLS + (threadIdx.x >> 2), part = threadIdx.x & 3;      // column, and which quarter of the key channels
+    const int j = blockIdx.z * DCOLS + (threadIdx.x >> 2), part = threadIdx.x & 3;      // column, and which run of key channels
     const int kh = h / (a.heads / a.kvh);
     const int row0 = a.req_start[req], n = a.req_start[req + 1] - row0;
     const int dim = a.dim, vdim = a.vdim;
@@ -914,14 +922,12 @@ delta_rule_kernel(DeltaArgs a) {
     float* S = a.state + (size_t)a.req_slot[req] * a.slot_stride + a.s_off + (size_t)h * dim * vdim;
     const bool live = j < vdim;
     const bool fresh = a.req_pos0[req] == 0;
+    const int d0 = part * DPT;                    // this lane's channels: d0 .. d0 + DPT - 1
     float s[DPT];
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) {
-        const int d = 4 * i + part;
-        s[i] = (live && !fresh && d < dim) ? S[(size_t)d * vdim + j] : 0.f;
-    }
-    // shared: two buffers of DCHUNK tokens, per token  q[dim] k[dim] g[dim] v[vdim] beta
-    const int per = 3 * dim + vdim + 1;
+    for (int i = 0; i < DPT; ++i) s[i] = (live && !fresh && d0 + i < dim) ? S[(size_t)(d0 + i) * vdim + j] : 0.f;
+    const int per = delta_token_floats(DPT, vdim);
+    const int o_k = 4 * RUN, o_g = 8 * RUN, o_v = 12 * RUN;
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     auto stage = [&](int c0, float* buf) {
         const int nc = min(DCHUNK, n - c0);
@@ -932,12 +938,13 @@ delta_rule_kernel(DeltaArgs a) {
             const float* g = a.decay + t * hd + (size_t)h * dim;
             const float* v = a.qkv + t * ch + 2 * qk + (size_t)h * vdim;
             for (int e = lane; e < dim; e += 32) {
-                cp_async4(dst + e, q + e);
-                cp_async4(dst + dim + e, q + qk + e);
-                cp_async4(dst + 2 * dim + e, g + e);
+                const int at = (e / DPT) * RUN + e % DPT;
+                cp_async4(dst + at, q + e);
+                cp_async4(dst + o_k + at, q + qk + e);
+                cp_async4(dst + o_g + at, g + e);
             }
-            for (int e = lane; e < vdim; e += 32) cp_async4(dst + 3 * dim + e, v + e);
-            if (lane == 0) cp_async4(dst + 3 * dim + vdim, a.beta + t * a.heads + h);
+            for (int e = lane; e < vdim; e += 32) cp_async4(dst + o_v + e, v + e);
+            if (lane == 0) cp_async4(dst + o_v + vdim, a.beta + t * a.heads + h);
         }
         cp_async_commit();
     };
@@ -951,24 +958,45 @@ delta_rule_kernel(DeltaArgs a) {
         if (c0 + DCHUNK < n) stage(c0 + DCHUNK, (it & 1) ? buf0 : buf1);
         const int nc = min(DCHUNK, n - c0);
         for (int tt = 0; tt < nc; ++tt) {
-            const float* q = cur + (size_t)tt * per;
-            const float* k = q + dim;
-            const float* g = k + dim;
-            float dot = 0.f;
+            const float* base = cur + (size_t)tt * per;
+            const float4* q4 = reinterpret_cast<const float4*>(base + part * RUN);
+            const float4* k4 = reinterpret_cast<const float4*>(base + o_k + part * RUN);
+            const float4* g4 = reinterpret_cast<const float4*>(base + o_g + part * RUN);
+            float dot0 = 0.f, dot1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const int d = 4 * i + part;
-                if (d < dim) { s[i] *= g[d]; dot = fmaf(s[i], k[d], dot); }
+            for (int i = 0; i < DPT; i += 4) {
+                if (FULL || d0 + i < dim) {
+                    const float4 gg = g4[i >> 2], kk = k4[i >> 2];
+                    const float ga[4] = {gg.x, gg.y, gg.z, gg.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (FULL || d0 + i + e < dim) {
+                            s[i + e] *= ga[e];
+                            if (e & 1) dot1 = fmaf(s[i + e], ka[e], dot1);
+                            else dot0 = fmaf(s[i + e], ka[e], dot0);
+                        }
+                }
             }
+            float dot = dot0 + dot1;
             dot += __shfl_xor_sync(0xffffffffu, dot, 1);
             dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            const float u = live ? g[dim + vdim] * (g[dim + j] - dot) : 0.f;
-            float o = 0.f;
+            const float u = live ? base[o_v + vdim] * (base[o_v + j] - dot) : 0.f;
+            float oa = 0.f, ob = 0.f;
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const int d = 4 * i + part;
-                if (d < dim) { s[i] = fmaf(k[d], u, s[i]); o = fmaf(s[i], q[d], o); }
+            for (int i = 0; i < DPT; i += 4) {
+                if (FULL || d0 + i < dim) {
+                    const float4 kk = k4[i >> 2], qq = q4[i >> 2];
+                    const float ka[4] = {kk.x, kk.y, kk.z, kk.w}, qa[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (FULL || d0 + i + e < dim) {
+                            s[i + e] = fmaf(ka[e], u, s[i + e]);
+                            if (e & 1) ob = fmaf(s[i + e], qa[e], ob);
+                            else oa = fmaf(s[i + e], qa[e], oa);
+                        }
+                }
             }
+            float o = oa + ob;
             o += __shfl_xor_sync(0xffffffffu, o, 1);
             o += __shfl_xor_sync(0xffffffffu, o, 2);
             if (live && part == 0) a.o[(size_t)(row0 + c0 + tt) * ((size_t)a.heads * vdim) + (size_t)h * vdim + j] = o;
@@ -976,10 +1004,8 @@ delta_rule_kernel(DeltaArgs a) {
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) {
-            const int d = 4 * i + part;
-            if (d < dim) S[(size_t)d * vdim + j] = s[i];
-        }
+        for (int i = 0; i < DPT; ++i)
+            if (d0 + i < dim) S[(size_t)(d0 + i) * vdim + j] = s[i];
     }
 }
 
@@ -1016,27 +1042,27 @@ int launch_delta(const DeltaArgs& a, const float* gate, const float* out_norm, f
         FT_CHECK_CUDA(cudaGetLastError());
     }
     const int threads = (4 * std::min(a.vdim, DCOLS) + 31) / 32 * 32;      // four lanes per state column, whole warps
-    const size_t smem = (size_t)2 * DCHUNK * (3 * a.dim + a.vdim + 1) * 4;
+    const int dpt = a.dim <= 32 ? 8 : a.dim <= 64 ? 16 : a.dim <= 128 ? 32 : 64;
+    const size_t smem = (size_t)2 * DCHUNK * delta_token_floats(dpt, a.vdim) * 4;
     const dim3 grid(n_req, a.heads, (a.vdim + DCOLS - 1) / DCOLS);
-#define FT_DELTA(DPT_)                                                                                          \
-    do {                                                                                                        \
-        if (threads <= 512) {                                                                                   \
-            if (smem > 48 * 1024)                                                                               \
-                FT_CHECK_CUDA(cudaFuncSetAttribute(delta_rule_kernel<DPT_, 512>,                                \
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
-            delta_rule_kernel<DPT_, 512><<<grid, threads, smem, stream>>>(a);                                   \
-        } else {                                                                                                \
-            if (smem > 48 * 1024)                                                                               \
-                FT_CHECK_CUDA(cudaFuncSetAttribute(delta_rule_kernel<DPT_, 1024>,                               \
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
-            delta_rule_kernel<DPT_, 1024><<<grid, threads, smem, stream>>>(a);                                  \
-        }                                                                                                       \
+#define FT_DELTA_ONE(DPT_, FULL_)                                                                           \
+    do {                                                                                                    \
+        if (smem > 48 * 1024)                                                                               \
+            FT_CHECK_CUDA(cudaFuncSetAttribute(delta_rule_kernel<DPT_, 4 * DCOLS, FULL_>,                   \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
+        delta_rule_kernel<DPT_, 4 * DCOLS, FULL_><<<grid, threads, smem, stream>>>(a);                      \
+    } while (0)
+#define FT_DELTA(DPT_)                                  \
+    do {                                                \
+        if (a.dim == 4 * DPT_) FT_DELTA_ONE(DPT_, true); \
+        else FT_DELTA_ONE(DPT_, false);                 \
     } while (0)
     if (a.dim <= 32) FT_DELTA(8);
     else if (a.dim <= 64) FT_DELTA(16);
     else if (a.dim <= 128) FT_DELTA(32);
     else FT_DELTA(64);
 #undef FT_DELTA
+#undef FT_DELTA_ONE
     FT_CHECK_CUDA(cudaGetLastError());
     const int n_pairs = T * a.heads;
     delta_out_kernel<<<(n_pairs + 3) / 4, 128, 0, stream>>>(a.o, gate, out_norm, a.vdim, eps, n_pairs);

@@ -77,11 +77,12 @@ MIXED = [delta(**moe()), latent(**moe(experts=6, top=3, groups=3, keep=2, ff=24)
     [delta()],
     [delta(heads=3, kv_heads=1, dim=40, vdim=72, conv=5, rank_a=3, rank_g=5)],
     [delta(heads=2, kv_heads=2, dim=8, vdim=8, conv=1)],
+    [delta(heads=2, kv_heads=1, dim=32, vdim=40, conv=3), delta(heads=3, kv_heads=3, dim=64, vdim=16, conv=2)],   # whole runs of channels per lane
     [latent(**moe())],                                 # experts: groups that matter, then one group, then top = all
     [latent(**moe(experts=6, top=2, groups=1, keep=1))],
     [latent(**moe(experts=4, top=4, groups=2, keep=2, ff=17))],
     MIXED,
-], ids=["latent", "delta", "delta-odd", "delta-conv1", "moe-groups", "moe-flat", "moe-all", "mixed"])
+], ids=["latent", "delta", "delta-odd", "delta-conv1", "delta-full-runs", "moe-groups", "moe-flat", "moe-all", "mixed"])
 def test_whole_prompt_matches_oracle(layers):
     spec, w = make(layers, seed=3)
     eng = engine(spec, w)
