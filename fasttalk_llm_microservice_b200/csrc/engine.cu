@@ -189,6 +189,10 @@ struct Layered {
     void *mx_hi = nullptr, *mx_lo = nullptr, *ax_hi = nullptr, *ax_lo = nullptr;
     float* gu = nullptr;
     int* h_seg = nullptr;
+    // the per-expert GEMMs are small (a few dozen CTAs): they are dealt over the engine's stream and three side streams
+    static constexpr int kSide = 3;
+    cudaStream_t side[kSide] = {};
+    cudaEvent_t side_done[kSide] = {}, main_ready = nullptr;
     bool tensor = false;               // projections that tile run on the tensor cores (ft_layered_model.exact_f32 == 0)
     float* trail = nullptr;            // debug: residual stream after every layer [n_layers][t_max][width]
     bool trail_on = false;
@@ -661,23 +665,37 @@ static int forward_layered(Engine* e, const Batch& b) {
                 auto off = [](const void* p, size_t elems) { return (const void*)((const uint8_t*)p + elems * 2); };
                 ft_gemm_epilogue ep = {};
                 ep.mode = FT_EPI_PARTIAL;
+                auto lane_of = [&](int k) { return k % (Layered::kSide + 1) == 0 ? st : L.side[k % (Layered::kSide + 1) - 1]; };
+                auto join = [&]() -> int {          // the engine's stream waits for what the side streams were given
+                    for (int k = 0; k < Layered::kSide; ++k) {
+                        FT_CHECK_CUDA(cudaEventRecord(L.side_done[k], L.side[k]));
+                        FT_CHECK_CUDA(cudaStreamWaitEvent(st, L.side_done[k], 0));
+                    }
+                    return 0;
+                };
+                int k = 0;                          // (the engine's stream is idle here: the side streams may start at once)
                 for (int x = 0; x < c.experts; ++x) {
                     const int r0 = L.h_seg[x], nr = L.h_seg[x + 1] - r0;
                     if (nr <= 0) continue;
                     ep.out = L.gu + (size_t)r0 * 2 * c.ff;
                     FT_TRY(ft_gemm_fused(off(c.w_gu, (size_t)x * 2 * c.ff * W), off(L.mx_hi, (size_t)r0 * W),
-                                         off(L.mx_lo, (size_t)r0 * W), 2 * c.ff, nr, W, 1, &ep, st));
+                                         off(L.mx_lo, (size_t)r0 * W), 2 * c.ff, nr, W, 1, &ep, lane_of(k++)));
                     launched();
                 }
+                FT_TRY(join());
                 FT_TRY(launch_swiglu_planes(L.gu, L.ax_hi, L.ax_lo, (size_t)pairs * c.ff, st));
+                FT_CHECK_CUDA(cudaEventRecord(L.main_ready, st));
+                for (int i = 0; i < Layered::kSide; ++i) FT_CHECK_CUDA(cudaStreamWaitEvent(L.side[i], L.main_ready, 0));
+                k = 0;
                 for (int x = 0; x < c.experts; ++x) {
                     const int r0 = L.h_seg[x], nr = L.h_seg[x + 1] - r0;
                     if (nr <= 0) continue;
                     ep.out = L.eout + (size_t)r0 * W;
                     FT_TRY(ft_gemm_fused(off(c.w_down, (size_t)x * W * c.ff), off(L.ax_hi, (size_t)r0 * c.ff),
-                                         off(L.ax_lo, (size_t)r0 * c.ff), W, nr, c.ff, 1, &ep, st));
+                                         off(L.ax_lo, (size_t)r0 * c.ff), W, nr, c.ff, 1, &ep, lane_of(k++)));
                     launched();
                 }
+                FT_TRY(join());
                 launched(4);
             } else {
             LinearArgs gu;                  // gate and up of every (token, choice) pair, grouped by expert
@@ -1301,6 +1319,13 @@ static int engine_init_layered(Engine* e) {
         for (const LayeredLayer& ll : L.layers) e_max = std::max(e_max, ll.d.experts);
         FT_TRY(alloc(&L.seg, (size_t)(e_max + 1) * 4));
         FT_CHECK_CUDA(cudaMallocHost(&L.h_seg, (size_t)(e_max + 1) * 4));
+        if (L.tensor) {
+            for (int k = 0; k < Layered::kSide; ++k) {
+                FT_CHECK_CUDA(cudaStreamCreateWithFlags(&L.side[k], cudaStreamNonBlocking));
+                FT_CHECK_CUDA(cudaEventCreateWithFlags(&L.side_done[k], cudaEventDisableTiming));
+            }
+            FT_CHECK_CUDA(cudaEventCreateWithFlags(&L.main_ready, cudaEventDisableTiming));
+        }
     }
     const size_t rows_last = std::max<size_t>(e->logit_rows, 256);
     e->rows_last = (int)rows_last;
@@ -1332,6 +1357,11 @@ static void engine_free(Engine* e) {
         cudaFree(L.slot_pos); cudaFree(L.trail); cudaFree(L.pl_hi); cudaFree(L.pl_lo); cudaFree(L.hn_hi); cudaFree(L.hn_lo);
         cudaFree(L.mx_hi); cudaFree(L.mx_lo); cudaFree(L.ax_hi); cudaFree(L.ax_lo); cudaFree(L.gu);
         if (L.h_seg) cudaFreeHost(L.h_seg);
+        for (int k = 0; k < Layered::kSide; ++k) {
+            if (L.side[k]) cudaStreamDestroy(L.side[k]);
+            if (L.side_done[k]) cudaEventDestroy(L.side_done[k]);
+        }
+        if (L.main_ready) cudaEventDestroy(L.main_ready);
         delete e->lay;
     }
     if (e->meta.h) cudaFreeHost(e->meta.h);
