@@ -1,0 +1,506 @@
+// Kernels of the branch mixers and of the sandwich layer form (ft_branch_desc, FT_LAYER_SANDWICH).  Everything here is
+// fp32: positions and angles, scores and softmax, norms, gates, decays and the recurrent state; the projections that feed
+// these kernels come from the linear / tensor-core GEMMs of the layered family.
+//
+//   sandwich norm        x += rms(y) * post_gain;  hn = rms(x) * next_gain   (y = scaled sum of up to two branch results, or
+//                        the experts' weighted sum plus the shared expert): one kernel between any two GEMMs of a layer
+//   window attention     biases + rotary pairs, rotated keys and values into the paged cache; one CTA per (token, head),
+//                        its warps take key blocks of the window in turn (one key per lane for the scores, one value column
+//                        per lane for the sum), online softmax, merged through shared memory
+//   scalar-decay rule    S <- a_t S + b_t k_t v_t^T, o_t = S^T q_t for a request's tokens in order; one CTA per (request,
+//                        head, block of value columns), LPC lanes share a column and hold a run of key channels of its
+//                        state in registers.  Decay attention, the gated matrix memory and the state-space mixer all run
+//                        on it; they differ in how a, b, q, k, v are prepared and in the read-out that follows
+//   preparation          SiLU in place; gate pre-activations and the running-maximum scan of the matrix memory; short causal
+//                        convolution over a step's rows and the slot's tail, step sizes and decays of the state space
+//   read-out             normaliser, skip, gates and group-wise RMS norm in one pass per (token, norm group)
+#include "common.cuh"
+#include "ft_internal.h"
+
+#include <algorithm>
+
+namespace ft {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+__device__ __forceinline__ float cta_sum(float v, float* red) {      // red: >= 33 floats of shared memory
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+__device__ __forceinline__ void put_planes(__nv_bfloat16* hi, __nv_bfloat16* lo, size_t i, float v) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    hi[i] = h;
+    lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+}
+
+// ------------------------------------------------------------------ sandwich norm
+__global__ void __launch_bounds__(256) sandwich_norm_kernel(SandwichArgs a) {
+    __shared__ float red[33];
+    extern __shared__ float row[];
+    const int t = blockIdx.x, W = a.W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float y = 0.f;
+        if (a.y0) y = a.s0 * a.y0[(size_t)t * W + c];
+        if (a.y1) y = fmaf(a.s1, a.y1[(size_t)t * W + c], y);
+        if (a.top > 0) {
+            float f = 0.f;
+            for (int k = 0; k < a.top; ++k)
+                f = fmaf(a.wt[(size_t)t * a.top + k], a.eout[(size_t)a.slot_pos[(size_t)t * a.top + k] * W + c], f);
+            y += f;
+        }
+        row[c] = y;
+        ss += y * y;
+    }
+    ss = cta_sum(ss, red);
+    const float r1 = 1.f / sqrtf(ss / (float)W + a.eps);
+    float s2 = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = a.x[(size_t)t * W + c] + row[c] * r1 * a.post_w[c];
+        a.x[(size_t)t * W + c] = v;
+        row[c] = v;
+        s2 += v * v;
+    }
+    s2 = cta_sum(s2, red);
+    const float r2 = 1.f / sqrtf(s2 / (float)W + a.eps);
+    __nv_bfloat16 *hi = (__nv_bfloat16*)a.hi, *lo = (__nv_bfloat16*)a.lo;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = row[c] * r2 * a.next_w[c];
+        a.hn[(size_t)t * W + c] = v;
+        if (hi) put_planes(hi, lo, (size_t)t * W + c, v);
+    }
+}
+
+int launch_sandwich_norm(const SandwichArgs& a, int T, cudaStream_t stream) {
+    FT_REQUIRE(a.x && a.hn && a.post_w && a.next_w && (a.y0 || a.y1 || a.top > 0), "sandwich norm: missing operands");
+    sandwich_norm_kernel<<<T, 256, (size_t)a.W * 4, stream>>>(a);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------ elementwise preparation
+// x[t][c0 .. c0 + n) <- silu(x) in place, rows of stride ld
+__global__ void silu_cols_kernel(float* __restrict__ x, int ld, int c0, int n) {
+    float* r = x + (size_t)blockIdx.x * ld + c0;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) r[c] = silu_f(r[c]);
+}
+int launch_silu_cols(float* x, int ld, int c0, int n, int T, cudaStream_t stream) {
+    silu_cols_kernel<<<T, 256, 0, stream>>>(x, ld, c0, n);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+// ab[t][h] = (decay[h], 1)
+__global__ void const_decay_kernel(const float* __restrict__ decay, float* __restrict__ ab, int heads, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { ab[2 * (size_t)i] = decay[i % heads]; ab[2 * (size_t)i + 1] = 1.f; }
+}
+int launch_const_decay(const float* decay, float* ab, int heads, int T, cudaStream_t stream) {
+    const int n = T * heads;
+    const_decay_kernel<<<(n + 255) / 256, 256, 0, stream>>>(decay, ab, heads, n);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------ window attention
+// Token t: q = proj[o_q ..] + bias, rotated, -> q_out; k = proj[o_k ..] + bias: the rotated key and the value (the key before
+// rotation, or proj[o_v ..]) -> the cache row of its position: [kv_heads * dim keys | kv_heads * vdim values].
+__device__ __forceinline__ float rotated(const float* __restrict__ src, const float* __restrict__ bias, int idx, int c,
+                                         int rot_dims, const float* __restrict__ freq, float pos) {
+    const float me = src[idx] + (bias ? bias[idx] : 0.f);
+    if (c >= rot_dims) return me;
+    const int other = idx ^ 1;                 // (2i, 2i+1) pairs; a head starts on an even index when dim is even
+    const float ot = src[other] + (bias ? bias[other] : 0.f);
+    float sn, cs;
+    sincosf(pos * freq[c >> 1], &sn, &cs);
+    return (c & 1) ? me * cs + ot * sn : me * cs - ot * sn;
+}
+__global__ void __launch_bounds__(128) window_write_kernel(WindowArgs a) {
+    const int t = blockIdx.x;
+    const float* pr = a.proj + (size_t)t * a.ldp;
+    const int p = a.positions[t];
+    const float pos = (float)p;
+    const int nq = a.H * a.dim, nk = a.G * a.dim, nv = a.G * a.vdim;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x)
+        a.q_out[(size_t)t * nq + i] = rotated(pr + a.o_q, a.q_bias, i, i % a.dim, a.rot_dims, a.rot_freq, pos);
+    const int* pt = a.page_table + (size_t)a.seq_rows[t] * a.max_pages;
+    float* row = a.cache + ((size_t)pt[p >> 6] * 64 + (p & 63)) * (size_t)(nk + nv);
+    for (int i = threadIdx.x; i < nk; i += blockDim.x)
+        row[i] = rotated(pr + a.o_k, a.k_bias, i, i % a.dim, a.rot_dims, a.rot_freq, pos);
+    for (int i = threadIdx.x; i < nv; i += blockDim.x)
+        row[nk + i] = a.o_v >= 0 ? pr[a.o_v + i] : pr[a.o_k + i] + (a.k_bias ? a.k_bias[i] : 0.f);
+}
+
+constexpr int kWinWarps = 4;
+template <int VPL, bool VEC>
+__global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs a) {
+    extern __shared__ float sh[];
+    float* sq = sh;                                    // [dim]
+    float* sm = sq + ((a.dim + 3) & ~3);               // [warps] running maxima
+    float* sl = sm + kWinWarps;                        // [warps] running sums
+    float* sacc = sl + kWinWarps;                      // [warps][vdim]
+    const int h = blockIdx.x, t = blockIdx.y;
+    const int g = h / (a.H / a.G);
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p = a.positions[t];
+    const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    const int n = p - lo + 1;
+    const int* pt = a.page_table + (size_t)a.seq_rows[t] * a.max_pages;
+    const size_t rowsz = (size_t)a.G * (a.dim + a.vdim);
+    for (int c = threadIdx.x; c < a.dim; c += blockDim.x) sq[c] = a.q_out[((size_t)t * a.H + h) * a.dim + c];
+    __syncthreads();
+    float m = -INFINITY, l = 0.f, acc[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
+    for (int b0 = wid * 32; b0 < n; b0 += kWinWarps * 32) {
+        const int j = lo + b0 + lane;
+        const bool valid = j <= p;
+        const int jj = valid ? j : p;
+        const long long base = ((long long)pt[jj >> 6] * 64 + (jj & 63)) * (long long)rowsz;
+        const float* kr = a.cache + base + (size_t)g * a.dim;
+        float s = 0.f;
+        if (VEC) {
+            for (int c = 0; c < a.dim; c += 4) {
+                const float4 kv = *reinterpret_cast<const float4*>(kr + c);
+                const float4 qv = *reinterpret_cast<const float4*>(sq + c);
+                s = fmaf(qv.x, kv.x, s); s = fmaf(qv.y, kv.y, s); s = fmaf(qv.z, kv.z, s); s = fmaf(qv.w, kv.w, s);
+            }
+        } else {
+            for (int c = 0; c < a.dim; ++c) s = fmaf(sq[c], kr[c], s);
+        }
+        s *= a.scale;
+        if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+        if (!valid) s = -INFINITY;
+        const float m_new = fmaxf(m, warp_max(s));
+        const float corr = expf(m - m_new);            // 0 on the first block (m = -inf)
+        const float pj = valid ? expf(s - m_new) : 0.f;
+        l = l * corr + warp_sum(pj);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) acc[i] *= corr;
+        m = m_new;
+        const int cnt = min(32, n - b0);
+        for (int x = 0; x < cnt; ++x) {
+            const float px = __shfl_sync(0xffffffffu, pj, x);
+            const long long bx = __shfl_sync(0xffffffffu, base, x);
+            const float* vr = a.cache + bx + (size_t)a.G * a.dim + (size_t)g * a.vdim;
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                const int c = lane + 32 * i;
+                if (c < a.vdim) acc[i] = fmaf(px, vr[c], acc[i]);
+            }
+        }
+    }
+    if (lane == 0) { sm[wid] = m; sl[wid] = l; }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int c = lane + 32 * i;
+        if (c < a.vdim) sacc[(size_t)wid * a.vdim + c] = acc[i];
+    }
+    __syncthreads();
+    float mm = sm[0];
+    for (int w = 1; w < kWinWarps; ++w) mm = fmaxf(mm, sm[w]);
+    float den = 0.f;
+    for (int w = 0; w < kWinWarps; ++w) den += sl[w] * expf(sm[w] - mm);
+    for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) {
+        float num = 0.f;
+        for (int w = 0; w < kWinWarps; ++w) num += sacc[(size_t)w * a.vdim + c] * expf(sm[w] - mm);
+        a.out[((size_t)t * a.H + h) * a.vdim + c] = num / den;
+    }
+}
+
+int launch_window_attention(const WindowArgs& a, int T, cudaStream_t stream) {
+    FT_REQUIRE(a.H >= 1 && a.G >= 1 && a.H % a.G == 0 && a.dim >= 1 && a.vdim >= 1 && a.vdim <= 256,
+               "window attention: bad head sizes (heads %d, kv heads %d, dim %d, vdim %d)", a.H, a.G, a.dim, a.vdim);
+    FT_REQUIRE(a.rot_dims >= 0 && a.rot_dims <= a.dim && (a.rot_dims & 1) == 0 && (a.rot_dims == 0 || (a.dim & 1) == 0),
+               "window attention: rotary pairs need even sizes (dim %d, rotated %d)", a.dim, a.rot_dims);
+    FT_REQUIRE(a.o_v >= 0 || a.vdim == a.dim, "window attention: keys used as values need vdim == dim");
+    window_write_kernel<<<T, 128, 0, stream>>>(a);
+    FT_CHECK_CUDA(cudaGetLastError());
+    const size_t smem = (size_t)(((a.dim + 3) & ~3) + 2 * kWinWarps + kWinWarps * a.vdim) * 4;
+    const bool vec = (a.dim & 3) == 0 && (a.vdim & 3) == 0;      // every key row then starts on 16 bytes
+    dim3 grid(a.H, T);
+    const int vpl = (a.vdim + 31) / 32;
+#define FT_WIN(V)                                                                                   \
+    do {                                                                                            \
+        if (vec) window_attn_kernel<V, true><<<grid, kWinWarps * 32, smem, stream>>>(a);            \
+        else window_attn_kernel<V, false><<<grid, kWinWarps * 32, smem, stream>>>(a);               \
+    } while (0)
+    if (vpl <= 1) FT_WIN(1);
+    else if (vpl <= 2) FT_WIN(2);
+    else if (vpl <= 4) FT_WIN(4);
+    else FT_WIN(8);
+#undef FT_WIN
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------ scalar-decay rule
+// Lanes s = 0..LPC-1 of a column hold channels s * DPT .. s * DPT + DPT - 1 of that column of S.  A chunk of RCH tokens is
+// staged in shared memory (keys and queries padded with zeros to LPC * DPT channels, each lane's run 4 floats apart from
+// the next so that the 16-byte reads of the LPC runs fall into different banks), then the tokens are taken in order.
+constexpr int RCH = 8, RTHREADS = 128;
+template <int LPC, int DPT>
+__global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
+    constexpr int VB = RTHREADS / LPC, RUN = DPT + 4, DP = LPC * RUN;
+    extern __shared__ __align__(16) float rs[];
+    float* sk = rs;                        // [RCH][DP]
+    float* sqq = sk + RCH * DP;            // [RCH][DP]
+    float* sv = sqq + RCH * DP;            // [RCH][VB]
+    float* sab = sv + RCH * VB;            // [RCH][2]
+    const int r = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * VB;
+    const int s = threadIdx.x % LPC, jl = threadIdx.x / LPC, j = j0 + jl;
+    const int t0 = a.req_start[r], t1 = a.req_start[r + 1];
+    if (t1 <= t0) return;
+    const int gh = h / (a.heads / a.qk_heads);
+    float* S = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.s_off + (size_t)h * a.dim * a.vd;
+    const bool live = j < a.vd;
+    float st[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = s * DPT + i;
+        st[i] = (a.req_pos0[r] > 0 && live && d < a.dim) ? S[(size_t)d * a.vd + j] : 0.f;
+    }
+    for (int c0 = t0; c0 < t1; c0 += RCH) {
+        const int nt = min(RCH, t1 - c0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * LPC * DPT; i += RTHREADS) {
+            const int tt = i / (LPC * DPT), d = i % (LPC * DPT);
+            const int at = tt * DP + (d / DPT) * RUN + (d % DPT);
+            const bool in = d < a.dim;
+            sk[at] = in ? a.k[(size_t)(c0 + tt) * a.ldk + (size_t)gh * a.dim + d] : 0.f;
+            sqq[at] = in ? a.q[(size_t)(c0 + tt) * a.ldq + (size_t)gh * a.dim + d] : 0.f;
+        }
+        for (int i = threadIdx.x; i < nt * VB; i += RTHREADS) {
+            const int tt = i / VB, c = i % VB;
+            sv[i] = j0 + c < a.vd ? a.v[(size_t)(c0 + tt) * a.ldv + (size_t)h * a.vd + j0 + c] : 0.f;
+        }
+        for (int i = threadIdx.x; i < nt * 2; i += RTHREADS)
+            sab[i] = a.ab[((size_t)(c0 + i / 2) * a.heads + h) * 2 + (i & 1)];
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float da = sab[2 * tt], bv = sab[2 * tt + 1] * sv[tt * VB + jl];
+            const float* kp = sk + tt * DP + s * RUN;
+            const float* qp = sqq + tt * DP + s * RUN;
+            float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT; i += 4) {
+                const float4 kv = *reinterpret_cast<const float4*>(kp + i);
+                const float4 qv = *reinterpret_cast<const float4*>(qp + i);
+                st[i] = fmaf(da, st[i], bv * kv.x);
+                st[i + 1] = fmaf(da, st[i + 1], bv * kv.y);
+                st[i + 2] = fmaf(da, st[i + 2], bv * kv.z);
+                st[i + 3] = fmaf(da, st[i + 3], bv * kv.w);
+                o0 = fmaf(st[i], qv.x, o0);
+                o1 = fmaf(st[i + 1], qv.y, o1);
+                o0 = fmaf(st[i + 2], qv.z, o0);
+                o1 = fmaf(st[i + 3], qv.w, o1);
+            }
+            float o = o0 + o1;
+#pragma unroll
+            for (int off = LPC / 2; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+            if (s == 0 && live) a.o[(size_t)(c0 + tt) * a.ldo + (size_t)h * a.vd + j] = o;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = s * DPT + i;
+            if (d < a.dim) S[(size_t)d * a.vd + j] = st[i];
+        }
+    }
+}
+
+template <int LPC, int DPT>
+static int launch_decay_rule_t(const RecurArgs& a, int n_req, cudaStream_t stream) {
+    constexpr int VB = RTHREADS / LPC, DP = LPC * (DPT + 4);
+    const size_t smem = (size_t)(2 * RCH * DP + RCH * VB + RCH * 2) * 4;
+    if (smem > 48 * 1024)
+        FT_CHECK_CUDA(cudaFuncSetAttribute(decay_rule_kernel<LPC, DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((a.vd + VB - 1) / VB, a.heads, n_req);
+    decay_rule_kernel<LPC, DPT><<<grid, RTHREADS, smem, stream>>>(a);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_decay_rule(const RecurArgs& a, int n_req, cudaStream_t stream) {
+    FT_REQUIRE(a.heads >= 1 && a.qk_heads >= 1 && a.heads % a.qk_heads == 0 && a.dim >= 1 && a.dim <= 1024 && a.vd >= 1,
+               "decay rule: bad sizes (heads %d, key heads %d, dim %d, values %d)", a.heads, a.qk_heads, a.dim, a.vd);
+    if (n_req <= 0) return 0;
+    if (a.dim <= 16) return launch_decay_rule_t<4, 4>(a, n_req, stream);
+    if (a.dim <= 32) return launch_decay_rule_t<4, 8>(a, n_req, stream);
+    if (a.dim <= 64) return launch_decay_rule_t<4, 16>(a, n_req, stream);
+    if (a.dim <= 128) return launch_decay_rule_t<4, 32>(a, n_req, stream);
+    if (a.dim <= 256) return launch_decay_rule_t<8, 32>(a, n_req, stream);
+    if (a.dim <= 512) return launch_decay_rule_t<16, 32>(a, n_req, stream);
+    return launch_decay_rule_t<32, 32>(a, n_req, stream);
+}
+
+// ------------------------------------------------------------------ gated matrix memory: gates and the running maximum
+// Per token: values with a column of ones appended (the normaliser rides along as one more state column), and the log
+// gates i = cap tanh((z_i + b_i) / cap), f = logsigmoid(cap tanh((z_f + b_f) / cap)).
+__global__ void __launch_bounds__(128) memory_prep_kernel(MemoryArgs a) {
+    const int t = blockIdx.x;
+    const float* pr = a.proj + (size_t)t * a.ldp;
+    const int ve = a.vdim + 1;
+    for (int i = threadIdx.x; i < a.heads * ve; i += blockDim.x) {
+        const int h = i / ve, j = i % ve;
+        a.v_ext[(size_t)t * a.heads * ve + i] = j < a.vdim ? pr[a.o_v + h * a.vdim + j] : 1.f;
+    }
+    for (int h = threadIdx.x; h < a.heads; h += blockDim.x) {
+        const float zi = pr[a.o_i + h] + a.gate_bias[h], zf = pr[a.o_f + h] + a.gate_bias[a.heads + h];
+        const float gi = a.cap * tanhf(zi / a.cap);
+        const float gf = -softplus_f(-(a.cap * tanhf(zf / a.cap)));
+        a.gates[((size_t)t * a.heads + h) * 2] = gi;
+        a.gates[((size_t)t * a.heads + h) * 2 + 1] = gf;
+    }
+}
+// One thread per (request, head) walks the request's tokens: m <- max(f + m, i); a = exp(f + m_old - m), b = exp(i - m);
+// floor[t] = exp(-m), the lower bound of the read-out's denominator.  m lives in the state slot, 0 at a sequence's start.
+__global__ void memory_scan_kernel(MemoryArgs a) {
+    const int r = blockIdx.x, h = threadIdx.x;
+    if (h >= a.heads) return;
+    const int t0 = a.req_start[r], t1 = a.req_start[r + 1];
+    if (t1 <= t0) return;
+    float* ms = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.m_off + h;
+    float m = a.req_pos0[r] > 0 ? *ms : 0.f;
+    for (int t = t0; t < t1; ++t) {
+        const size_t at = (size_t)t * a.heads + h;
+        const float gi = a.gates[2 * at], gf = a.gates[2 * at + 1];
+        const float mn = fmaxf(gf + m, gi);
+        a.ab[2 * at] = expf(gf + m - mn);
+        a.ab[2 * at + 1] = expf(gi - mn);
+        a.floor[at] = expf(-mn);
+        m = mn;
+    }
+    *ms = m;
+}
+int launch_memory_prep(const MemoryArgs& a, int T, int n_req, cudaStream_t stream) {
+    FT_REQUIRE(a.heads >= 1 && a.heads <= 1024 && a.cap > 0.f, "matrix memory: bad head count or gate cap");
+    memory_prep_kernel<<<T, 128, 0, stream>>>(a);
+    FT_CHECK_CUDA(cudaGetLastError());
+    memory_scan_kernel<<<n_req, ((a.heads + 31) / 32) * 32, 0, stream>>>(a);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------ state space: convolution, step sizes, tails
+// u = raw x | B | C channels of a token (proj columns o_x ..).  out[t][c] = silu(bias[c] + sum_j w[c][K-1-j] u[t-j][c]); rows
+// before the step's first come from the slot's tail (the last K-1 raw inputs of the sequence), zeros before position 0.
+__global__ void __launch_bounds__(256) space_conv_kernel(SpaceArgs a) {
+    const int t = blockIdx.x;
+    const int r = a.seq_rows[t];
+    const int start = a.req_start[r], pos0 = a.req_pos0[r], K = a.taps;
+    const int k = t - start;
+    const float* tail = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.tail_off;
+    for (int c = threadIdx.x; c < a.channels; c += blockDim.x) {
+        float acc = a.conv_b ? a.conv_b[c] : 0.f;
+        for (int j = 0; j < K; ++j) {
+            float u = 0.f;
+            if (k - j >= 0) u = a.proj[(size_t)(t - j) * a.ldp + a.o_x + c];
+            else if (pos0 + k - j >= 0) u = tail[(size_t)c * (K - 1) + (k - j + K - 1)];
+            acc = fmaf(a.conv_w[(size_t)c * K + (K - 1 - j)], u, acc);
+        }
+        a.xbc[(size_t)t * a.channels + c] = silu_f(acc);
+    }
+    for (int h = threadIdx.x; h < a.heads; h += blockDim.x) {
+        const float dt = softplus_f(a.proj[(size_t)t * a.ldp + a.o_dt + h] + a.dt_bias[h]);
+        a.ab[((size_t)t * a.heads + h) * 2] = expf(-expf(a.a_log[h]) * dt);
+        a.ab[((size_t)t * a.heads + h) * 2 + 1] = dt;
+    }
+}
+// The slot's tail after the step: the raw inputs of the last K-1 positions, from this step's rows or the old tail.
+constexpr int kMaxTaps = 16;
+__global__ void __launch_bounds__(256) space_tail_kernel(SpaceArgs a) {
+    const int r = blockIdx.x;
+    const int start = a.req_start[r], n = a.req_start[r + 1] - start, pos0 = a.req_pos0[r], K = a.taps;
+    if (n <= 0 || K <= 1) return;
+    float* tail = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.tail_off;
+    for (int c = threadIdx.x; c < a.channels; c += blockDim.x) {
+        float nv[kMaxTaps];
+        for (int i = 0; i < K - 1; ++i) {
+            const int k = n - (K - 1) + i;
+            float u = 0.f;
+            if (k >= 0) u = a.proj[(size_t)(start + k) * a.ldp + a.o_x + c];
+            else if (pos0 + k >= 0) u = tail[(size_t)c * (K - 1) + (k + K - 1)];
+            nv[i] = u;
+        }
+        for (int i = 0; i < K - 1; ++i) tail[(size_t)c * (K - 1) + i] = nv[i];
+    }
+}
+int launch_space_prep(const SpaceArgs& a, int T, int n_req, cudaStream_t stream) {
+    FT_REQUIRE(a.taps >= 1 && a.taps <= kMaxTaps, "state space: 1 to %d convolution taps (got %d)", kMaxTaps, a.taps);
+    space_conv_kernel<<<T, 256, 0, stream>>>(a);
+    FT_CHECK_CUDA(cudaGetLastError());
+    space_tail_kernel<<<n_req, 256, 0, stream>>>(a);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------ read-out of the recurrent branches
+// One warp per (token, norm group).  Value of column c = (head h, j):
+//   o[t][h * vd + j] * q_scale                              (vd = vdim, or vdim + 1 with the normaliser in the last column)
+//   / (max(|o[t][h * vd + vdim] * q_scale|, floor[t][h]) + 1e-6)      with a normaliser
+//   + skip[h] * x[t][c]                                      with a skip
+//   * silu(gate[t][c])                                       gate_kind 1 (before the norm)
+// then divided by the root mean square of its group, times gain[c], times sigmoid(gate[t][c]) for gate_kind 2.
+__device__ __forceinline__ float readout_value(const ReadoutArgs& a, int t, int c) {
+    const int h = c / a.vdim, j = c % a.vdim;
+    const float* orow = a.o + (size_t)t * a.ldo + (size_t)h * a.vd;
+    float v = orow[j] * a.q_scale;
+    if (a.floor) v = v / (fmaxf(fabsf(orow[a.vdim] * a.q_scale), a.floor[(size_t)t * a.heads + h]) + 1e-6f);
+    if (a.skip) v = fmaf(a.skip[h], a.x[(size_t)t * a.ldx + c], v);
+    if (a.gate_kind == 1) v *= silu_f(a.gate[(size_t)t * a.ldg + c]);
+    return v;
+}
+__global__ void __launch_bounds__(128) readout_kernel(ReadoutArgs a, int n_units) {
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (unit >= n_units) return;
+    const int t = unit / a.norm_groups, g = unit % a.norm_groups;
+    const int n = a.heads * a.vdim / a.norm_groups, c0 = g * n;
+    float ss = 0.f;
+    for (int c = lane; c < n; c += 32) { const float v = readout_value(a, t, c0 + c); ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    const float rr = 1.f / sqrtf(ss / (float)n + a.eps);
+    for (int c = lane; c < n; c += 32) {
+        float v = readout_value(a, t, c0 + c) * rr * a.gain[c0 + c];
+        if (a.gate_kind == 2) v *= sigmoid_f(a.gate[(size_t)t * a.ldg + c0 + c]);
+        a.out[(size_t)t * a.heads * a.vdim + c0 + c] = v;
+    }
+}
+int launch_readout(const ReadoutArgs& a, int T, cudaStream_t stream) {
+    FT_REQUIRE(a.norm_groups >= 1 && (a.heads * a.vdim) % a.norm_groups == 0, "read-out: %d columns do not split into %d norm groups",
+               a.heads * a.vdim, a.norm_groups);
+    const int units = T * a.norm_groups;
+    readout_kernel<<<(units + 3) / 4, 128, 0, stream>>>(a, units);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------ activations between the two halves of a feed-forward
+// SwiGLU: gu [rows][2 ff] with columns (2j, 2j+1) = (gate_j, up_j) -> out [rows][ff]; squared ReLU: [rows][ff] -> [rows][ff]
+__global__ void ff_act_kernel(const float* __restrict__ in, float* __restrict__ out, size_t n, int act) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        if (act == FT_ACT_RELU2) { const float v = fmaxf(in[i], 0.f); out[i] = v * v; }
+        else { const float2 v = reinterpret_cast<const float2*>(in)[i]; out[i] = silu_f(v.x) * v.y; }
+    }
+}
+int launch_ff_act(const float* in, float* out, size_t n, int act, cudaStream_t stream) {
+    const int blocks = (int)std::min<size_t>((n + 255) / 256, 148 * 16);
+    ff_act_kernel<<<blocks, 256, 0, stream>>>(in, out, n, act);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace ft

@@ -169,18 +169,26 @@ struct LayeredLayer {
     ft_layer_desc d;
     size_t cache_off = 0;              // floats: this layer's [num_pages][64][kv_rank] block in lat_cache
     size_t s_off = 0, tail_off = 0;    // floats inside a state slot: S [heads][dim][vdim], tails [channels][conv - 1]
+    // branch mixers: per branch its block in kv_cache (window attention), its S inside a state slot, and what else it keeps
+    // there (the running maximum of a matrix memory, the convolution tails of a state space)
+    size_t br_cache_off[2] = {0, 0}, br_s_off[2] = {0, 0}, br_x_off[2] = {0, 0};
 };
 struct Layered {
     ft_layered_model m;
     std::vector<LayeredLayer> layers;
     float* lat_cache = nullptr;
     void* lat_cache16 = nullptr;       // serving form: bf16 copy of the latents, same places (tensor-core attention)
+    float* kv_cache = nullptr;         // window-attention branches: per layer [num_pages][64][kv_heads * (dim + vdim)] fp32
     float* state = nullptr;
     size_t slot_stride = 0;            // floats per state slot
     int n_stateful = 0;                // layers whose mixer carries state from token to token
     int ld_proj = 0, top_max = 0;
     float *hn = nullptr, *proj = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *b4 = nullptr, *beta = nullptr,
           *attn_part = nullptr, *mix = nullptr, *act = nullptr, *eout = nullptr, *wts = nullptr, *xlast = nullptr;
+    // branch mixers and sandwich layers: queries, prepared values, rule outputs, read-out, (decay, input) pairs, log gates,
+    // denominator floors, the second branch's projection, feed-forward halves, router logits
+    float *bq = nullptr, *bv = nullptr, *bo = nullptr, *bfin = nullptr, *ab = nullptr, *gates = nullptr, *floor = nullptr,
+          *mix2 = nullptr, *ffa = nullptr, *ffb = nullptr, *rlog = nullptr;
     int *ids = nullptr, *seg = nullptr, *slot_token = nullptr, *slot_pos = nullptr;
     void *pl_hi = nullptr, *pl_lo = nullptr;      // bf16 planes of a projection's input [t_max][k_max]
     void *hn_hi = nullptr, *hn_lo = nullptr;      // bf16 planes of the normed layer input [t_max][width]
@@ -583,9 +591,176 @@ static int dense(Engine* e, const float* A, const void* hi, const void* lo, cons
     return 0;
 }
 
+// The mixture of experts of one layer: routing from `logits` (row stride ldl, first column o_router), then every (token,
+// choice) pair through its expert, grouped by expert.  Reads the rows of L.hn; leaves the pairs' outputs in L.eout and their
+// weights / places in L.wts / L.slot_pos (the caller's residual kernel gathers them).
+static int run_experts(Engine* e, const ft_layer_desc& c, const float* logits, int ldl, int o_router, int T) {
+    Layered& L = *e->lay;
+    const int W = L.m.width;
+    cudaStream_t st = e->stream;
+    auto launched = [&](int n = 1) { e->st.kernel_launches += n; };
+    const bool sandwich = c.form == FT_LAYER_SANDWICH;
+    const int act = sandwich ? c.ff_act : FT_ACT_SWIGLU;
+    const int n_up = act == FT_ACT_SWIGLU ? 2 * c.ff : c.ff;          // rows of an expert's first matrix
+    const int top = c.top;
+    FT_TRY(launch_route(logits, ldl, o_router, c.experts, c.top, sandwich ? 1 : c.groups, sandwich ? 1 : c.keep, L.ids, L.wts,
+                        L.seg, L.slot_token, L.slot_pos, T, st, sandwich ? c.route_kind : FT_ROUTE_SOFTMAX,
+                        sandwich ? c.route_norm : 0, sandwich ? c.route_scale : 1.f));
+    const int pairs = T * top;
+    const bool on_tensor = L.tensor && pairs >= kMoeTensorMinPairs && n_up % 128 == 0 && c.ff % 64 == 0 && W % 128 == 0 &&
+                           W % 64 == 0;
+    if (on_tensor) {
+        // One tcgen05 GEMM per expert over its run of sorted rows.  The launches need the run lengths on the host:
+        // a copy of E + 1 integers and a wait, a few microseconds against the milliseconds of such a step.
+        FT_CHECK_CUDA(cudaMemcpyAsync(L.h_seg, L.seg, (size_t)(c.experts + 1) * 4, cudaMemcpyDeviceToHost, st));
+        FT_TRY(launch_gather_planes_rows(L.hn, L.slot_token, L.mx_hi, L.mx_lo, pairs, W, st));
+        FT_CHECK_CUDA(cudaStreamSynchronize(st));
+        auto off = [](const void* p, size_t elems) { return (const void*)((const uint8_t*)p + elems * 2); };
+        ft_gemm_epilogue ep = {};
+        ep.mode = FT_EPI_PARTIAL;
+        auto lane_of = [&](int k) { return k % (Layered::kSide + 1) == 0 ? st : L.side[k % (Layered::kSide + 1) - 1]; };
+        auto join = [&]() -> int {          // the engine's stream waits for what the side streams were given
+            for (int k = 0; k < Layered::kSide; ++k) {
+                FT_CHECK_CUDA(cudaEventRecord(L.side_done[k], L.side[k]));
+                FT_CHECK_CUDA(cudaStreamWaitEvent(st, L.side_done[k], 0));
+            }
+            return 0;
+        };
+        FT_CHECK_CUDA(cudaEventRecord(L.main_ready, st));
+        for (int i = 0; i < Layered::kSide; ++i) FT_CHECK_CUDA(cudaStreamWaitEvent(L.side[i], L.main_ready, 0));
+        int k = 0;
+        for (int x = 0; x < c.experts; ++x) {
+            const int r0 = L.h_seg[x], nr = L.h_seg[x + 1] - r0;
+            if (nr <= 0) continue;
+            ep.out = L.gu + (size_t)r0 * n_up;
+            FT_TRY(ft_gemm_fused(off(c.w_gu, (size_t)x * n_up * W), off(L.mx_hi, (size_t)r0 * W),
+                                 off(L.mx_lo, (size_t)r0 * W), n_up, nr, W, 1, &ep, lane_of(k++)));
+            launched();
+        }
+        FT_TRY(join());
+        FT_TRY(launch_swiglu_planes(L.gu, L.ax_hi, L.ax_lo, (size_t)pairs * c.ff, st, act));
+        FT_CHECK_CUDA(cudaEventRecord(L.main_ready, st));
+        for (int i = 0; i < Layered::kSide; ++i) FT_CHECK_CUDA(cudaStreamWaitEvent(L.side[i], L.main_ready, 0));
+        k = 0;
+        for (int x = 0; x < c.experts; ++x) {
+            const int r0 = L.h_seg[x], nr = L.h_seg[x + 1] - r0;
+            if (nr <= 0) continue;
+            ep.out = L.eout + (size_t)r0 * W;
+            FT_TRY(ft_gemm_fused(off(c.w_down, (size_t)x * W * c.ff), off(L.ax_hi, (size_t)r0 * c.ff),
+                                 off(L.ax_lo, (size_t)r0 * c.ff), W, nr, c.ff, 1, &ep, lane_of(k++)));
+            launched();
+        }
+        FT_TRY(join());
+        launched(4);
+    } else {
+        LinearArgs gu;                  // first matrix of every (token, choice) pair, grouped by expert, with its activation
+        gu.A = L.hn; gu.a_rows = L.slot_token; gu.lda = W; gu.W = (const __nv_bfloat16*)c.w_gu;
+        gu.w_stride = (long long)n_up * W; gu.ldw = W; gu.C = L.act; gu.ldc = c.ff; gu.seg = L.seg;
+        gu.N = n_up; gu.K = W; gu.P = c.experts; gu.epi = act == FT_ACT_SWIGLU ? LIN_SWIGLU_PAIR : LIN_RELU2;
+        FT_TRY(launch_linear(gu, T * top, st));
+        LinearArgs dn;
+        dn.A = L.act; dn.lda = c.ff; dn.W = (const __nv_bfloat16*)c.w_down; dn.w_stride = (long long)W * c.ff;
+        dn.ldw = c.ff; dn.C = L.eout; dn.ldc = W; dn.seg = L.seg; dn.N = W; dn.K = c.ff; dn.P = c.experts;
+        FT_TRY(launch_linear(dn, T * top, st));
+    }
+    launched(4);
+    return 0;
+}
+
+// out [T][width] = W_down act(W_up in) for every row: the dense feed-forward and the shared expert of a sandwich layer.
+// `in` is the normed stream L.hn (hi / lo: its planes when the step has them).
+static int run_mlp(Engine* e, const void* hi, const void* lo, const void* w_up, const void* w_down, int ff, int act, float* out,
+                   int T) {
+    Layered& L = *e->lay;
+    const int W = L.m.width;
+    const int n_up = act == FT_ACT_SWIGLU ? 2 * ff : ff;
+    cudaStream_t st = e->stream;
+    if (L.tensor && T >= kTensorMinRows && n_up % 128 == 0 && W % 64 == 0 && W % 128 == 0 && ff % 64 == 0) {
+        FT_TRY(dense(e, L.hn, hi, lo, w_up, L.ffa, T, n_up, W));
+        FT_TRY(launch_swiglu_planes(L.ffa, L.ax_hi, L.ax_lo, (size_t)T * ff, st, act));
+        e->st.kernel_launches++;
+        return dense(e, nullptr, L.ax_hi, L.ax_lo, w_down, out, T, W, ff);
+    }
+    LinearArgs up;
+    up.A = L.hn; up.lda = W; up.W = (const __nv_bfloat16*)w_up; up.ldw = W; up.C = L.ffb; up.ldc = ff; up.M = T; up.N = n_up;
+    up.K = W; up.epi = act == FT_ACT_SWIGLU ? LIN_SWIGLU_PAIR : LIN_RELU2;
+    FT_TRY(launch_linear(up, T, st));
+    e->st.kernel_launches++;
+    return dense(e, L.ffb, nullptr, nullptr, w_down, out, T, W, ff);
+}
+
+// One branch of a branch mixer: from the layer's stacked projection L.proj to `y` [T][width] (before its out_scale).
+static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, float* y) {
+    Layered& L = *e->lay;
+    const ft_layered_model& M = L.m;
+    const ft_branch_desc& c = ll.d.branch[k];
+    StepMeta& m = e->meta;
+    int* d = m.d;
+    const int T = b.T, ld = ll.d.n_in;
+    cudaStream_t st = e->stream;
+    auto launched = [&](int n = 1) { e->st.kernel_launches += n; };
+    const float* fin = L.bfin;
+    if (c.kind == FT_BRANCH_WINDOW_ATTENTION) {
+        WindowArgs a;
+        a.proj = L.proj; a.ldp = ld; a.o_q = c.o_q; a.o_k = c.o_k; a.o_v = c.o_v;
+        a.q_bias = c.q_bias; a.k_bias = c.k_bias; a.rot_freq = c.rot_freq; a.rot_dims = c.rot_dims;
+        a.q_out = L.bq; a.cache = L.kv_cache + ll.br_cache_off[k];
+        a.positions = d + m.o_pos; a.seq_rows = d + m.o_rows; a.page_table = d + m.o_pt; a.max_pages = e->max_pages;
+        a.H = c.heads; a.G = c.kv_heads; a.dim = c.dim; a.vdim = c.vdim; a.window = c.window;
+        a.scale = c.scale; a.softcap = c.softcap; a.out = L.bfin;
+        FT_TRY(launch_window_attention(a, T, st));
+        launched(2);
+    } else {
+        RecurArgs r;
+        r.ab = L.ab; r.o = L.bo; r.state = L.state; r.slot_stride = (long long)L.slot_stride; r.s_off = (long long)ll.br_s_off[k];
+        r.req_start = d + m.o_xstart; r.req_pos0 = d + m.o_xpos0; r.req_slot = d + m.o_xslot;
+        r.heads = c.heads; r.qk_heads = c.kv_heads; r.dim = c.dim; r.vd = c.vdim; r.ldo = c.heads * c.vdim;
+        ReadoutArgs o;
+        o.o = L.bo; o.vd = c.vdim; o.vdim = c.vdim; o.heads = c.heads; o.gain = c.out_norm; o.eps = M.eps; o.out = L.bfin;
+        if (c.kind == FT_BRANCH_DECAY_ATTENTION) {
+            // q | k | v are adjacent columns of the projection: SiLU in place, then the rule reads them where they are
+            FT_TRY(launch_silu_cols(L.proj, ld, c.o_q, 2 * c.kv_heads * c.dim + c.heads * c.vdim, T, st));
+            FT_TRY(launch_const_decay(c.decay, L.ab, c.heads, T, st));
+            r.q = L.proj + c.o_q; r.k = L.proj + c.o_k; r.v = L.proj + c.o_v; r.ldq = r.ldk = r.ldv = ld;
+            o.gate = L.proj + c.o_g; o.ldg = ld; o.gate_kind = 2; o.norm_groups = 1;
+            launched(2);
+        } else if (c.kind == FT_BRANCH_MATRIX_MEMORY) {
+            MemoryArgs g;
+            g.proj = L.proj; g.ldp = ld; g.o_v = c.o_v; g.o_i = c.o_i; g.o_f = c.o_f; g.gate_bias = c.gate_bias; g.cap = c.gate_cap;
+            g.heads = c.heads; g.vdim = c.vdim; g.v_ext = L.bv; g.gates = L.gates; g.ab = L.ab; g.floor = L.floor;
+            g.state = L.state; g.slot_stride = (long long)L.slot_stride; g.m_off = (long long)ll.br_x_off[k];
+            g.req_start = r.req_start; g.req_pos0 = r.req_pos0; g.req_slot = r.req_slot;
+            FT_TRY(launch_memory_prep(g, T, b.n_req, st));
+            r.q = L.proj + c.o_q; r.k = L.proj + c.o_k; r.ldq = r.ldk = ld;
+            r.v = L.bv; r.vd = c.vdim + 1; r.ldv = r.ldo = c.heads * (c.vdim + 1);
+            o.vd = c.vdim + 1; o.q_scale = 1.f / sqrtf((float)c.dim); o.floor = L.floor;
+            o.gate = L.proj + c.o_g; o.ldg = ld; o.gate_kind = 2; o.norm_groups = c.heads;
+            launched(2);
+        } else {
+            const int inner = c.heads * c.vdim, gn = c.kv_heads * c.dim;
+            SpaceArgs s;
+            s.proj = L.proj; s.ldp = ld; s.o_x = c.o_v; s.o_dt = c.o_dt; s.channels = inner + 2 * gn; s.taps = c.conv;
+            s.heads = c.heads; s.conv_w = c.conv_w; s.conv_b = c.conv_b; s.dt_bias = c.dt_bias; s.a_log = c.a_log;
+            s.xbc = L.bv; s.ab = L.ab; s.state = L.state; s.slot_stride = (long long)L.slot_stride;
+            s.tail_off = (long long)ll.br_x_off[k];
+            s.seq_rows = d + m.o_rows; s.req_start = r.req_start; s.req_pos0 = r.req_pos0; s.req_slot = r.req_slot;
+            FT_TRY(launch_space_prep(s, T, b.n_req, st));
+            r.v = L.bv; r.k = L.bv + inner; r.q = L.bv + inner + gn; r.ldq = r.ldk = r.ldv = s.channels;
+            o.skip = c.skip; o.x = L.bv; o.ldx = s.channels;
+            o.gate = L.proj + c.o_z; o.ldg = ld; o.gate_kind = 1; o.norm_groups = c.norm_groups;
+            launched(2);
+        }
+        o.ldo = r.ldo;
+        FT_TRY(launch_decay_rule(r, b.n_req, st));
+        FT_TRY(launch_readout(o, T, st));
+        launched(2);
+    }
+    return dense(e, fin, nullptr, nullptr, c.w_o, y, T, M.width, c.heads * c.vdim);
+}
+
 // Forward pass of a layered model.  Per layer: ONE projection of the normed input into all the parts that read it
-// (queries, latents or q/k/v, gates, low-rank inner products, residual gates, router logits), the mixer, the experts, and
-// one kernel that updates the residual stream and norms it for the next layer.
+// (queries, latents or q/k/v, gates, low-rank inner products, residual gates, router logits), the mixer, the feed-forward, and
+// one kernel per sublayer joint that updates the residual stream and norms it for what reads it next.
 static int forward_layered(Engine* e, const Batch& b) {
     Layered& L = *e->lay;
     const ft_layered_model& M = L.m;
@@ -596,13 +771,26 @@ static int forward_layered(Engine* e, const Batch& b) {
     void* hn_hi = L.tensor && T >= kTensorMinRows ? L.hn_hi : nullptr;      // planes of the normed input, written by its producer
     void* hn_lo = hn_hi ? L.hn_lo : nullptr;
     auto launched = [&](int n = 1) { e->st.kernel_launches += n; };
-    FT_TRY(launch_embed_norm(d + m.o_tokens, M.embed, e->resid, L.hn, hn_hi, hn_lo, T, W, M.eps, L.layers[0].d.norm_gain, st));
+    FT_TRY(launch_embed_norm(d + m.o_tokens, M.embed, e->resid, L.hn, hn_hi, hn_lo, T, W, M.eps, L.layers[0].d.norm_gain,
+                             L.layers[0].d.form == FT_LAYER_SANDWICH ? L.layers[0].d.norm_pre1 : nullptr, st));
     launched();
     for (int l = 0; l < M.n_layers; ++l) {
         const LayeredLayer& ll = L.layers[l];
         const ft_layer_desc& c = ll.d;
+        const bool sandwich = c.form == FT_LAYER_SANDWICH;
         const int ld = c.n_in;              // row stride of this layer's projection outputs
         FT_TRY(dense(e, L.hn, hn_hi, hn_lo, c.w_in, L.proj, T, c.n_in, W));
+        const float *y0 = L.mix, *y1 = nullptr;      // the mixer's result: s0 * y0 + s1 * y1, each [T][width]
+        float s0 = 1.f, s1 = 1.f;
+        if (c.mixer == FT_MIXER_BRANCHES) {
+            FT_TRY(run_branch(e, b, ll, 0, L.mix));
+            s0 = c.branch[0].out_scale;
+            if (c.n_branches > 1) {
+                FT_TRY(run_branch(e, b, ll, 1, L.mix2));
+                y1 = L.mix2;
+                s1 = c.branch[1].out_scale;
+            }
+        } else {
         const float* mixed = nullptr;      // [T][heads * vdim], input of the output projection
         if (c.mixer == FT_MIXER_LATENT_ATTENTION) {
             float* cache = L.lat_cache + ll.cache_off;
@@ -648,72 +836,53 @@ static int forward_layered(Engine* e, const Batch& b) {
             mixed = L.b4;
         }
         FT_TRY(dense(e, mixed, nullptr, nullptr, c.w_o, L.mix, T, W, c.heads * c.vdim));
-        int top = 0;
-        if (c.ff_kind == FT_FF_MOE) {
-            top = c.top;
-            FT_TRY(launch_route(L.proj, ld, c.o_router, c.experts, c.top, c.groups, c.keep, L.ids, L.wts, L.seg,
-                                L.slot_token, L.slot_pos, T, st));
-            const int pairs = T * top;
-            const bool on_tensor = L.tensor && pairs >= kMoeTensorMinPairs && (2 * c.ff) % 128 == 0 && c.ff % 64 == 0 &&
-                                   W % 128 == 0;
-            if (on_tensor) {
-                // One tcgen05 GEMM per expert over its run of sorted rows.  The launches need the run lengths on the host:
-                // a copy of E + 1 integers and a wait, a few microseconds against the milliseconds of such a step.
-                FT_CHECK_CUDA(cudaMemcpyAsync(L.h_seg, L.seg, (size_t)(c.experts + 1) * 4, cudaMemcpyDeviceToHost, st));
-                FT_TRY(launch_gather_planes_rows(L.hn, L.slot_token, L.mx_hi, L.mx_lo, pairs, W, st));
-                FT_CHECK_CUDA(cudaStreamSynchronize(st));
-                auto off = [](const void* p, size_t elems) { return (const void*)((const uint8_t*)p + elems * 2); };
-                ft_gemm_epilogue ep = {};
-                ep.mode = FT_EPI_PARTIAL;
-                auto lane_of = [&](int k) { return k % (Layered::kSide + 1) == 0 ? st : L.side[k % (Layered::kSide + 1) - 1]; };
-                auto join = [&]() -> int {          // the engine's stream waits for what the side streams were given
-                    for (int k = 0; k < Layered::kSide; ++k) {
-                        FT_CHECK_CUDA(cudaEventRecord(L.side_done[k], L.side[k]));
-                        FT_CHECK_CUDA(cudaStreamWaitEvent(st, L.side_done[k], 0));
-                    }
-                    return 0;
-                };
-                int k = 0;                          // (the engine's stream is idle here: the side streams may start at once)
-                for (int x = 0; x < c.experts; ++x) {
-                    const int r0 = L.h_seg[x], nr = L.h_seg[x + 1] - r0;
-                    if (nr <= 0) continue;
-                    ep.out = L.gu + (size_t)r0 * 2 * c.ff;
-                    FT_TRY(ft_gemm_fused(off(c.w_gu, (size_t)x * 2 * c.ff * W), off(L.mx_hi, (size_t)r0 * W),
-                                         off(L.mx_lo, (size_t)r0 * W), 2 * c.ff, nr, W, 1, &ep, lane_of(k++)));
-                    launched();
-                }
-                FT_TRY(join());
-                FT_TRY(launch_swiglu_planes(L.gu, L.ax_hi, L.ax_lo, (size_t)pairs * c.ff, st));
-                FT_CHECK_CUDA(cudaEventRecord(L.main_ready, st));
-                for (int i = 0; i < Layered::kSide; ++i) FT_CHECK_CUDA(cudaStreamWaitEvent(L.side[i], L.main_ready, 0));
-                k = 0;
-                for (int x = 0; x < c.experts; ++x) {
-                    const int r0 = L.h_seg[x], nr = L.h_seg[x + 1] - r0;
-                    if (nr <= 0) continue;
-                    ep.out = L.eout + (size_t)r0 * W;
-                    FT_TRY(ft_gemm_fused(off(c.w_down, (size_t)x * W * c.ff), off(L.ax_hi, (size_t)r0 * c.ff),
-                                         off(L.ax_lo, (size_t)r0 * c.ff), W, nr, c.ff, 1, &ep, lane_of(k++)));
-                    launched();
-                }
-                FT_TRY(join());
-                launched(4);
-            } else {
-            LinearArgs gu;                  // gate and up of every (token, choice) pair, grouped by expert
-            gu.A = L.hn; gu.a_rows = L.slot_token; gu.lda = W; gu.W = (const __nv_bfloat16*)c.w_gu;
-            gu.w_stride = (long long)2 * c.ff * W; gu.ldw = W; gu.C = L.act; gu.ldc = c.ff; gu.seg = L.seg;
-            gu.N = 2 * c.ff; gu.K = W; gu.P = c.experts; gu.epi = LIN_SWIGLU_PAIR;
-            FT_TRY(launch_linear(gu, T * top, st));
-            LinearArgs dn;
-            dn.A = L.act; dn.lda = c.ff; dn.W = (const __nv_bfloat16*)c.w_down; dn.w_stride = (long long)W * c.ff;
-            dn.ldw = c.ff; dn.C = L.eout; dn.ldc = W; dn.seg = L.seg; dn.N = W; dn.K = c.ff; dn.P = c.experts;
-            FT_TRY(launch_linear(dn, T * top, st));
-            }
-            launched(4);
         }
-        const float gain_next = l + 1 < M.n_layers ? L.layers[l + 1].d.norm_gain : M.final_norm_gain;
-        FT_TRY(launch_combine_norm(e->resid, L.hn, L.proj, ld, c.o_rg1, c.o_rg2, c.rg_bias, L.mix, L.eout, L.wts,
-                                   L.slot_pos, top, T, W, M.eps, gain_next, hn_hi, hn_lo, st));
-        launched();
+        const ft_layer_desc* nx = l + 1 < M.n_layers ? &L.layers[l + 1].d : nullptr;
+        // gains of the norm that the next layer (or the head) reads: one number, or one per coordinate
+        const float gain_next = nx ? nx->norm_gain : M.final_norm_gain;
+        const float* gain_next_w = nx ? (nx->form == FT_LAYER_SANDWICH ? nx->norm_pre1 : nullptr) : M.final_norm_w;
+        if (sandwich) {
+            FT_REQUIRE(gain_next_w, "engine: layer %d: a sandwich layer needs per-coordinate gains in what follows it", l);
+            SandwichArgs sa;
+            sa.x = e->resid; sa.hn = L.hn; sa.hi = hn_hi; sa.lo = hn_lo; sa.W = W; sa.eps = M.eps;
+            sa.y0 = y0; sa.s0 = s0; sa.y1 = y1; sa.s1 = s1; sa.post_w = c.norm_post1;
+            sa.next_w = c.ff_kind != FT_FF_NONE ? c.norm_pre2 : gain_next_w;
+            FT_TRY(launch_sandwich_norm(sa, T, st));
+            launched();
+            if (c.ff_kind != FT_FF_NONE) {
+                SandwichArgs sf;
+                sf.x = e->resid; sf.hn = L.hn; sf.hi = hn_hi; sf.lo = hn_lo; sf.W = W; sf.eps = M.eps;
+                sf.post_w = c.norm_post2; sf.next_w = gain_next_w;
+                if (c.ff_kind == FT_FF_DENSE) {
+                    FT_TRY(run_mlp(e, hn_hi, hn_lo, c.w_gu, c.w_down, c.ff, c.ff_act, L.mix, T));
+                    sf.y0 = L.mix;
+                } else {
+                    LinearArgs r;                   // router logits in fp32, whatever the form of the other products
+                    r.A = L.hn; r.lda = W; r.W = (const __nv_bfloat16*)c.w_router; r.ldw = W; r.C = L.rlog; r.ldc = c.experts;
+                    r.M = T; r.N = c.experts; r.K = W;
+                    FT_TRY(launch_linear(r, T, st));
+                    launched();
+                    FT_TRY(run_experts(e, c, L.rlog, c.experts, 0, T));
+                    sf.eout = L.eout; sf.wt = L.wts; sf.slot_pos = L.slot_pos; sf.top = c.top;
+                    if (c.shared_ff > 0) {
+                        FT_TRY(run_mlp(e, hn_hi, hn_lo, c.w_shared_up, c.w_shared_down, c.shared_ff, c.ff_act, L.mix, T));
+                        sf.y0 = L.mix;
+                    }
+                }
+                FT_TRY(launch_sandwich_norm(sf, T, st));
+                launched();
+            }
+        } else {
+            int top = 0;
+            if (c.ff_kind == FT_FF_MOE) {
+                top = c.top;
+                FT_TRY(run_experts(e, c, L.proj, ld, c.o_router, T));
+            }
+            FT_REQUIRE(!gain_next_w, "engine: layer %d: a gated layer is followed by a norm with one gain", l);
+            FT_TRY(launch_combine_norm(e->resid, L.hn, L.proj, ld, c.o_rg1, c.o_rg2, c.rg_bias, L.mix, L.eout, L.wts,
+                                       L.slot_pos, top, T, W, M.eps, gain_next, hn_hi, hn_lo, st));
+            launched();
+        }
         if (L.trail_on && L.trail)
             FT_CHECK_CUDA(cudaMemcpyAsync(L.trail + (size_t)l * e->t_max * W, e->resid, (size_t)T * W * 4,
                                           cudaMemcpyDeviceToDevice, st));
@@ -1231,16 +1400,79 @@ static int engine_init_layered(Engine* e) {
 
     // sizes over all layers; places of each layer in the latent cache and in a state slot
     size_t cache_floats = 0, buf = 1, act_cols = 1;
+    size_t kv_floats = 0, br_q = 0, br_v = 0, br_o = 0, br_fin = 0, br_heads = 0, e_max_s = 1;
     int n_in_max = 1, top_max = 1, heads_max = 1, rank_max = 0;
     for (int l = 0; l < M.n_layers; ++l) {
         LayeredLayer& ll = L.layers[l];
         const ft_layer_desc& d = ll.d;
-        FT_REQUIRE(d.heads >= 1 && d.dim >= 1 && d.vdim >= 1 && d.n_in >= 1 && d.w_in && d.w_o && d.rg_bias && d.o_rg1 >= 0,
-                   "engine: layer %d is incomplete", l);
+        FT_REQUIRE(d.n_in >= 1 && d.w_in, "engine: layer %d is incomplete", l);
+        const bool sandwich = d.form == FT_LAYER_SANDWICH;
+        if (sandwich) {
+            FT_REQUIRE(d.norm_pre1 && d.norm_post1 && (d.ff_kind == FT_FF_NONE || (d.norm_pre2 && d.norm_post2)),
+                       "engine: sandwich layer %d lacks norm gains", l);
+        } else {
+            FT_REQUIRE(d.form == FT_LAYER_GATED && d.rg_bias && d.o_rg1 >= 0 && d.mixer != FT_MIXER_BRANCHES,
+                       "engine: gated layer %d is incomplete (it takes latent attention or channel delta)", l);
+        }
         n_in_max = std::max(n_in_max, d.n_in);
-        heads_max = std::max(heads_max, d.heads);
-        buf = std::max(buf, (size_t)d.heads * d.vdim);
-        if (d.mixer == FT_MIXER_LATENT_ATTENTION) {
+        if (d.mixer != FT_MIXER_BRANCHES) {
+            FT_REQUIRE(d.heads >= 1 && d.dim >= 1 && d.vdim >= 1 && d.w_o, "engine: layer %d is incomplete", l);
+            heads_max = std::max(heads_max, d.heads);
+            buf = std::max(buf, (size_t)d.heads * d.vdim);
+        }
+        if (d.mixer == FT_MIXER_BRANCHES) {
+            FT_REQUIRE(d.n_branches == 1 || d.n_branches == 2, "engine: layer %d has %d branches", l, d.n_branches);
+            for (int k = 0; k < d.n_branches; ++k) {
+                const ft_branch_desc& c = d.branch[k];
+                FT_REQUIRE(c.heads >= 1 && c.kv_heads >= 1 && c.heads % c.kv_heads == 0 && c.dim >= 1 && c.vdim >= 1 && c.w_o &&
+                               c.o_q >= 0 && c.o_k >= 0,
+                           "engine: layer %d branch %d is incomplete", l, k);
+                const size_t hv = (size_t)c.heads * c.vdim;
+                br_heads = std::max(br_heads, (size_t)c.heads);
+                br_fin = std::max(br_fin, hv);
+                if (c.kind == FT_BRANCH_WINDOW_ATTENTION) {
+                    FT_REQUIRE(c.window >= 0 && (c.rot_dims == 0 || c.rot_freq), "engine: layer %d branch %d: bad window or rotation", l, k);
+                    ll.br_cache_off[k] = kv_floats;
+                    kv_floats += (size_t)e->cfg.num_pages * kKvTile * c.kv_heads * (c.dim + c.vdim);
+                    br_q = std::max(br_q, (size_t)c.heads * c.dim);
+                } else if (c.kind == FT_BRANCH_DECAY_ATTENTION) {
+                    FT_REQUIRE(c.kv_heads == c.heads && c.decay && c.out_norm && c.o_v >= 0 && c.o_g >= 0 &&
+                                   c.o_k == c.o_q + c.heads * c.dim && c.o_v == c.o_k + c.heads * c.dim,
+                               "engine: decay-attention layer %d branch %d is incomplete", l, k);
+                    ll.br_s_off[k] = L.slot_stride;
+                    L.slot_stride += (size_t)c.heads * c.dim * c.vdim;
+                    br_o = std::max(br_o, hv);
+                    L.n_stateful++;
+                } else if (c.kind == FT_BRANCH_MATRIX_MEMORY) {
+                    FT_REQUIRE(c.kv_heads == c.heads && c.gate_bias && c.gate_cap > 0.f && c.out_norm && c.o_v >= 0 && c.o_g >= 0 &&
+                                   c.o_i >= 0 && c.o_f >= 0,
+                               "engine: matrix-memory layer %d branch %d is incomplete", l, k);
+                    ll.br_s_off[k] = L.slot_stride;
+                    L.slot_stride += (size_t)c.heads * c.dim * (c.vdim + 1);
+                    ll.br_x_off[k] = L.slot_stride;
+                    L.slot_stride += (size_t)c.heads;
+                    br_v = std::max(br_v, (size_t)c.heads * (c.vdim + 1));
+                    br_o = std::max(br_o, (size_t)c.heads * (c.vdim + 1));
+                    L.n_stateful++;
+                } else if (c.kind == FT_BRANCH_STATE_SPACE) {
+                    const size_t ch = hv + (size_t)2 * c.kv_heads * c.dim;
+                    FT_REQUIRE(c.conv >= 1 && c.conv_w && c.dt_bias && c.a_log && c.out_norm && c.norm_groups >= 1 &&
+                                   c.o_v >= 0 && c.o_z >= 0 && c.o_dt >= 0 && c.o_k == c.o_v + (int)hv &&
+                                   c.o_q == c.o_k + c.kv_heads * c.dim,
+                               "engine: state-space layer %d branch %d is incomplete", l, k);
+                    ll.br_s_off[k] = L.slot_stride;
+                    L.slot_stride += (size_t)c.heads * c.dim * c.vdim;
+                    ll.br_x_off[k] = L.slot_stride;
+                    L.slot_stride += ch * (size_t)std::max(c.conv - 1, 0);
+                    br_v = std::max(br_v, ch);
+                    br_o = std::max(br_o, hv);
+                    L.n_stateful++;
+                } else {
+                    FT_REQUIRE(false, "engine: layer %d branch %d has an unknown kind %d", l, k, c.kind);
+                }
+                L.slot_stride = (L.slot_stride + 3) & ~size_t(3);
+            }
+        } else if (d.mixer == FT_MIXER_LATENT_ATTENTION) {
             FT_REQUIRE(d.kv_rank >= 1 && d.w_uk_t && d.w_uv && d.dkv_norm && d.o_q >= 0 && d.o_dkv >= 0 && d.o_gate >= 0,
                        "engine: latent-attention layer %d is incomplete", l);
             ll.cache_off = cache_floats;
@@ -1264,9 +1496,16 @@ static int engine_init_layered(Engine* e) {
             FT_REQUIRE(false, "engine: layer %d has an unknown mixer %d", l, d.mixer);
         }
         if (d.ff_kind == FT_FF_MOE) {
-            FT_REQUIRE(d.experts >= 1 && d.top >= 1 && d.ff >= 1 && d.w_gu && d.w_down && d.o_router >= 0 && d.o_rg2 >= 0,
+            FT_REQUIRE(d.experts >= 1 && d.top >= 1 && d.top <= d.experts && d.ff >= 1 && d.w_gu && d.w_down &&
+                           (sandwich ? d.w_router != nullptr : d.o_router >= 0 && d.o_rg2 >= 0),
                        "engine: mixture-of-experts layer %d is incomplete", l);
+            FT_REQUIRE(!sandwich || d.shared_ff == 0 || (d.w_shared_up && d.w_shared_down),
+                       "engine: layer %d lacks the shared expert's weights", l);
             top_max = std::max(top_max, d.top);
+            act_cols = std::max(act_cols, (size_t)std::max(d.ff, sandwich ? d.shared_ff : 0));
+            e_max_s = std::max(e_max_s, (size_t)d.experts);
+        } else if (d.ff_kind == FT_FF_DENSE) {
+            FT_REQUIRE(sandwich && d.ff >= 1 && d.w_gu && d.w_down, "engine: dense feed-forward layer %d is incomplete", l);
             act_cols = std::max(act_cols, (size_t)d.ff);
         } else {
             FT_REQUIRE(d.ff_kind == FT_FF_NONE, "engine: layer %d has an unknown feed-forward %d", l, d.ff_kind);
@@ -1286,6 +1525,21 @@ static int engine_init_layered(Engine* e) {
     FT_TRY(alloc(&L.lat_cache, cache_floats * 4));
     if (M.exact_f32 == 0) FT_TRY(alloc(&L.lat_cache16, cache_floats * 2));
     FT_TRY(alloc(&L.state, L.slot_stride * (size_t)c.max_sessions * 4));
+    if (kv_floats) FT_TRY(alloc(&L.kv_cache, kv_floats * 4));
+    if (br_fin) {
+        FT_TRY(alloc(&L.bq, T * br_q * 4));
+        FT_TRY(alloc(&L.bv, T * br_v * 4));
+        FT_TRY(alloc(&L.bo, T * br_o * 4));
+        FT_TRY(alloc(&L.bfin, T * br_fin * 4));
+        FT_TRY(alloc(&L.ab, T * br_heads * 2 * 4));
+        FT_TRY(alloc(&L.gates, T * br_heads * 2 * 4));
+        FT_TRY(alloc(&L.floor, T * br_heads * 4));
+        FT_TRY(alloc(&L.mix2, T * W * 4));
+        buf = std::max(buf, br_fin);               // the planes of an output projection's input
+    }
+    FT_TRY(alloc(&L.ffa, T * act_cols * 2 * 4));
+    FT_TRY(alloc(&L.ffb, T * act_cols * 4));
+    FT_TRY(alloc(&L.rlog, T * e_max_s * 4));
     FT_TRY(alloc(&e->resid, T * W * 4));
     FT_TRY(alloc(&L.hn, T * W * 4));
     FT_TRY(alloc(&L.proj, T * L.ld_proj * 4));
@@ -1353,6 +1607,8 @@ static void engine_free(Engine* e) {
         Layered& L = *e->lay;
         cudaFree(L.lat_cache); cudaFree(L.lat_cache16); cudaFree(L.state); cudaFree(L.hn); cudaFree(L.proj); cudaFree(L.b1); cudaFree(L.b2);
         cudaFree(L.b3); cudaFree(L.b4); cudaFree(L.beta); cudaFree(L.attn_part); cudaFree(L.mix); cudaFree(L.act); cudaFree(L.eout);
+        cudaFree(L.kv_cache); cudaFree(L.bq); cudaFree(L.bv); cudaFree(L.bo); cudaFree(L.bfin); cudaFree(L.ab); cudaFree(L.gates);
+        cudaFree(L.floor); cudaFree(L.mix2); cudaFree(L.ffa); cudaFree(L.ffb); cudaFree(L.rlog);
         cudaFree(L.wts); cudaFree(L.xlast); cudaFree(L.ids); cudaFree(L.seg); cudaFree(L.slot_token);
         cudaFree(L.slot_pos); cudaFree(L.trail); cudaFree(L.pl_hi); cudaFree(L.pl_lo); cudaFree(L.hn_hi); cudaFree(L.hn_lo);
         cudaFree(L.mx_hi); cudaFree(L.mx_lo); cudaFree(L.ax_hi); cudaFree(L.ax_lo); cudaFree(L.gu);

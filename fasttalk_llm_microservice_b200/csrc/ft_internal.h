@@ -89,13 +89,14 @@ int launch_attn_prefill_tc(const void* q, int q_rows, const void* kv_layer, cons
                            cudaStream_t stream);
 
 // ---- layered.cu (the layered model family: every size is a run-time value, activations fp32, weights bf16)
-enum { LIN_PLAIN = 0, LIN_SWIGLU_PAIR = 1, LIN_SOFTCAP = 2 };
+enum { LIN_PLAIN = 0, LIN_SWIGLU_PAIR = 1, LIN_SOFTCAP = 2, LIN_RELU2 = 3 };
 // C[r, n] = sum_k A[row(r), k] * W[p][n, k] for problems p = 0..P-1.
 //   batched (seg == null): every problem has rows 0..M-1; problem p reads A + p * a_col_stride, W + p * w_stride and
 //                          writes C + p * c_col_stride (heads side by side in the columns of one buffer)
 //   grouped (seg != null): problem p owns rows seg[p]..seg[p+1]-1 of C; row r reads A row a_rows[r] (or r)
 // LIN_SWIGLU_PAIR: W rows (2j, 2j+1) are (gate_j, up_j); C[r, j] = silu(gate) * up, ldc counts those N/2 columns.
 // LIN_SOFTCAP:     C = cap * tanh(C / cap).
+// LIN_RELU2:       C = max(C, 0)^2.
 struct LinearArgs {
     const float* A = nullptr;
     const int* a_rows = nullptr;
@@ -110,12 +111,14 @@ struct LinearArgs {
 // rows_bound: M when batched; an upper bound of seg[P] when grouped
 int launch_linear(const LinearArgs& a, int rows_bound, cudaStream_t stream);
 // hi / lo (may be null): the normed row once more as bf16 planes, the input form of the tensor-core projections
+// gain_w (may be null): a gain per coordinate instead of the single `gain`
 int launch_embed_norm(const int* tokens, const void* embed, float* x, float* hn, void* hi, void* lo, int T, int W, float eps,
-                      float gain, cudaStream_t stream);
+                      float gain, const float* gain_w, cudaStream_t stream);
 int launch_to_planes(const float* x, void* hi, void* lo, size_t n, cudaStream_t stream);
 int launch_softcap(float* x, size_t n, float cap, cudaStream_t stream);
 int launch_gather_planes_rows(const float* src, const int* idx, void* hi, void* lo, int n, int W, cudaStream_t stream);
-int launch_swiglu_planes(const float* gu, void* hi, void* lo, size_t n, cudaStream_t stream);
+// act FT_ACT_SWIGLU: gu holds (gate, up) pairs, n counts pairs; FT_ACT_RELU2: gu holds n plain values
+int launch_swiglu_planes(const float* gu, void* hi, void* lo, size_t n, cudaStream_t stream, int act = FT_ACT_SWIGLU);
 int launch_combine_norm(float* x, float* hn, const float* proj, int ldp, int o_rg1, int o_rg2, const float* rg_bias,
                         const float* mix, const float* eout, const float* wt, const int* slot_pos, int top, int T, int W,
                         float eps, float gain, void* hi, void* lo, cudaStream_t stream);
@@ -157,7 +160,107 @@ struct DeltaArgs {
 int launch_delta(const DeltaArgs& a, const float* gate, const float* out_norm, float eps, int T, int n_req,
                  cudaStream_t stream);
 int launch_route(const float* proj, int ldp, int o_router, int E, int top, int groups, int keep, int* ids, float* wts,
-                 int* seg, int* slot_token, int* slot_pos, int T, cudaStream_t stream);
+                 int* seg, int* slot_token, int* slot_pos, int T, cudaStream_t stream, int route_kind = FT_ROUTE_SOFTMAX,
+                 int normalise = 0, float scale = 1.f);
+
+// ---- branches.cu (branch mixers and the sandwich layer form: ft_branch_desc, FT_LAYER_SANDWICH; everything fp32)
+// x += rms(y) * post_w;  hn = rms(x) * next_w  with  y = s0 * y0 + s1 * y1 + sum_k wt[t, k] * eout[slot_pos[t, k]]
+// (each of the three parts optional); hi / lo (may be null): hn once more as bf16 planes.
+struct SandwichArgs {
+    float* x = nullptr;
+    float* hn = nullptr;
+    void *hi = nullptr, *lo = nullptr;
+    const float *y0 = nullptr, *y1 = nullptr;
+    float s0 = 1.f, s1 = 1.f;
+    const float* eout = nullptr;
+    const float* wt = nullptr;
+    const int* slot_pos = nullptr;
+    int top = 0;
+    const float *post_w = nullptr, *next_w = nullptr;
+    int W = 0;
+    float eps = 0.f;
+};
+int launch_sandwich_norm(const SandwichArgs& a, int T, cudaStream_t stream);
+int launch_silu_cols(float* x, int ld, int c0, int n, int T, cudaStream_t stream);
+int launch_const_decay(const float* decay, float* ab, int heads, int T, cudaStream_t stream);
+int launch_ff_act(const float* in, float* out, size_t n, int act, cudaStream_t stream);
+
+// Softmax attention over the last `window` positions (0 = all) of a paged cache whose rows hold, per position,
+// [G * dim rotated keys | G * vdim values].  launch_window_attention writes the step's rows first, then attends.
+struct WindowArgs {
+    const float* proj = nullptr;
+    int ldp = 0, o_q = 0, o_k = 0, o_v = -1;      // o_v < 0: the values are the keys before rotation
+    const float *q_bias = nullptr, *k_bias = nullptr, *rot_freq = nullptr;
+    int rot_dims = 0;
+    float* q_out = nullptr;                       // [T][H * dim] work buffer
+    float* cache = nullptr;                       // this layer's [pages][64][G * (dim + vdim)]
+    const int *positions = nullptr, *seq_rows = nullptr, *page_table = nullptr;
+    int max_pages = 0;
+    int H = 0, G = 0, dim = 0, vdim = 0, window = 0;
+    float scale = 1.f, softcap = 0.f;
+    float* out = nullptr;                         // [T][H * vdim]
+};
+int launch_window_attention(const WindowArgs& a, int T, cudaStream_t stream);
+
+// S <- a_t S + b_t k_t v_t^T, o_t = S^T q_t per (request, head) over the request's rows in order; S [dim][vd] of head h at
+// state + slot * slot_stride + s_off + h * dim * vd, zero at a sequence's start (req_pos0 == 0).
+struct RecurArgs {
+    const float *q = nullptr, *k = nullptr, *v = nullptr;      // rows of stride ldq / ldk / ldv; q, k: qk_heads x dim, v: heads x vd
+    int ldq = 0, ldk = 0, ldv = 0;
+    const float* ab = nullptr;                    // [T][heads][2]
+    float* o = nullptr;                           // rows of stride ldo: heads x vd
+    int ldo = 0;
+    float* state = nullptr;
+    long long slot_stride = 0, s_off = 0;
+    const int *req_start = nullptr, *req_pos0 = nullptr, *req_slot = nullptr;
+    int heads = 0, qk_heads = 0, dim = 0, vd = 0;
+};
+int launch_decay_rule(const RecurArgs& a, int n_req, cudaStream_t stream);
+
+struct MemoryArgs {                               // gated matrix memory: what precedes the rule
+    const float* proj = nullptr;
+    int ldp = 0, o_v = 0, o_i = 0, o_f = 0;
+    const float* gate_bias = nullptr;             // [2 * heads]
+    float cap = 0.f;
+    int heads = 0, vdim = 0;
+    float* v_ext = nullptr;                       // out [T][heads][vdim + 1]
+    float* gates = nullptr;                       // out [T][heads][2]: log input gate, log forget gate
+    float* ab = nullptr;                          // out [T][heads][2]
+    float* floor = nullptr;                       // out [T][heads]: exp(-m_t)
+    float* state = nullptr;
+    long long slot_stride = 0, m_off = 0;         // m [heads] of this layer inside a slot
+    const int *req_start = nullptr, *req_pos0 = nullptr, *req_slot = nullptr;
+};
+int launch_memory_prep(const MemoryArgs& a, int T, int n_req, cudaStream_t stream);
+
+struct SpaceArgs {                                // state space: convolution + SiLU, step sizes and decays, new tails
+    const float* proj = nullptr;
+    int ldp = 0, o_x = 0, o_dt = 0, channels = 0, taps = 0, heads = 0;
+    const float *conv_w = nullptr, *conv_b = nullptr, *dt_bias = nullptr, *a_log = nullptr;
+    float* xbc = nullptr;                         // out [T][channels]
+    float* ab = nullptr;                          // out [T][heads][2]
+    float* state = nullptr;
+    long long slot_stride = 0, tail_off = 0;      // tails [channels][taps - 1] of this layer inside a slot
+    const int *seq_rows = nullptr, *req_start = nullptr, *req_pos0 = nullptr, *req_slot = nullptr;
+};
+int launch_space_prep(const SpaceArgs& a, int T, int n_req, cudaStream_t stream);
+
+struct ReadoutArgs {
+    const float* o = nullptr;                     // rows of stride ldo: heads x vd
+    int ldo = 0, vd = 0, vdim = 0, heads = 0;
+    float q_scale = 1.f;
+    const float* floor = nullptr;                 // non-null: column vdim of every head is the normaliser
+    const float* skip = nullptr;                  // [heads], with x rows of stride ldx
+    const float* x = nullptr;
+    int ldx = 0;
+    const float* gate = nullptr;                  // rows of stride ldg
+    int ldg = 0, gate_kind = 0;                   // 0 none, 1 silu before the norm, 2 sigmoid after it
+    int norm_groups = 1;
+    const float* gain = nullptr;                  // [heads * vdim]
+    float eps = 0.f;
+    float* out = nullptr;                         // [T][heads * vdim]
+};
+int launch_readout(const ReadoutArgs& a, int T, cudaStream_t stream);
 
 // ---- sampling.cu
 int launch_sample(const float* logits, int B, int V, const float* temperature, const int* top_k,

@@ -148,6 +148,7 @@ __global__ void __launch_bounds__(LTHREADS) linear_tile_kernel(LinearArgs a) {
                 if (n < a.N) {
                     float v = acc[i][j];
                     if (a.epi == LIN_SOFTCAP) v = a.cap * tanhf(v / a.cap);
+                    else if (a.epi == LIN_RELU2) { v = fmaxf(v, 0.f); v *= v; }
                     C[(size_t)r * a.ldc + n] = v;
                 }
             }
@@ -255,6 +256,7 @@ __global__ void __launch_bounds__(LWARPS * 32) linear_rows_kernel(LinearArgs a) 
                 } else {
                     v = warp_sum(acc[c][i]);
                     if (a.epi == LIN_SOFTCAP) v = a.cap * tanhf(v / a.cap);
+                    else if (a.epi == LIN_RELU2) { v = fmaxf(v, 0.f); v *= v; }
                 }
                 if (lane == 0 && col0 + c < cols) C[(size_t)(rb + i) * a.ldc + col0 + c] = v;
             }
@@ -333,14 +335,24 @@ __global__ void swiglu_planes_kernel(const float* __restrict__ gu, __nv_bfloat16
     }
 }
 
+// u [rows][ff]  ->  planes of relu(u)^2
+__global__ void relu2_planes_kernel(const float* __restrict__ u, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+                                    size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = fmaxf(u[i], 0.f);
+        store_planes(hi, lo, i, v * v);
+    }
+}
+
 int launch_gather_planes_rows(const float* src, const int* idx, void* hi, void* lo, int n, int W, cudaStream_t stream) {
     gather_planes_kernel2<<<n, 256, 0, stream>>>(src, idx, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, W);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
-int launch_swiglu_planes(const float* gu, void* hi, void* lo, size_t n, cudaStream_t stream) {
+int launch_swiglu_planes(const float* gu, void* hi, void* lo, size_t n, cudaStream_t stream, int act) {
     const int blocks = (int)std::min<size_t>((n + 255) / 256, 148 * 16);
-    swiglu_planes_kernel<<<blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, n);
+    if (act == FT_ACT_RELU2) relu2_planes_kernel<<<blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, n);
+    else swiglu_planes_kernel<<<blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, n);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -363,7 +375,7 @@ int launch_softcap(float* x, size_t n, float cap, cudaStream_t stream) {
 __global__ void __launch_bounds__(256)
 embed_norm_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ embed, float* __restrict__ x,
                   float* __restrict__ hn, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo, int W, float eps,
-                  float gain) {
+                  float gain, const float* __restrict__ gain_w) {
     __shared__ float red[33];
     const int t = blockIdx.x;
     const __nv_bfloat16* e = embed + (size_t)tokens[t] * W;
@@ -376,7 +388,8 @@ embed_norm_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restric
     ss = block_sum(ss, red);
     const float r = gain / sqrtf(ss / (float)W + eps);
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float v = __bfloat162float(e[c]) * r;
+        float v = __bfloat162float(e[c]) * r;
+        if (gain_w) v *= gain_w[c];
         hn[(size_t)t * W + c] = v;
         if (hi) store_planes(hi, lo, (size_t)t * W + c, v);
     }
@@ -424,9 +437,9 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __r
 }
 
 int launch_embed_norm(const int* tokens, const void* embed, float* x, float* hn, void* hi, void* lo, int T, int W, float eps,
-                      float gain, cudaStream_t stream) {
+                      float gain, const float* gain_w, cudaStream_t stream) {
     embed_norm_kernel<<<T, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)embed, x, hn, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo,
-                                             W, eps, gain);
+                                             W, eps, gain_w ? 1.f : gain, gain_w);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -1071,11 +1084,12 @@ int launch_delta(const DeltaArgs& a, const float* gate, const float* out_norm, f
 }
 
 // ------------------------------------------------------------------ router
-// One warp per token: s = softmax(z) over all E experts; a group's score is its largest s; only experts of the `keep`
-// best groups can be chosen; the `top` largest s among them, lowest index first on a tie; weights = s as it is.
+// One warp per token: s = softmax(z) over all E experts (or sigmoid(z) of each); a group's score is its largest s; only
+// experts of the `keep` best groups can be chosen; the `top` largest s among them, lowest index first on a tie; weights = s
+// as it is, or (normalise) divided by the sum of the chosen ones (+ 1e-20); then times `scale`.
 __global__ void __launch_bounds__(128)
 route_kernel(const float* __restrict__ proj, int ldp, int o_router, int E, int top, int groups, int keep, int* __restrict__ ids,
-             float* __restrict__ wts, int T) {
+             float* __restrict__ wts, int T, int sigmoid_scores, int normalise, float scale) {
     extern __shared__ float sh[];
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + wid;
@@ -1083,14 +1097,18 @@ route_kernel(const float* __restrict__ proj, int ldp, int o_router, int E, int t
     float* s = sh + (size_t)wid * (E + groups);     // scores, then group scores; a taken entry is set to -1
     float* gs = s + E;
     const float* z = proj + (size_t)t * ldp + o_router;
-    float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) { const float v = expf(z[e] - m); s[e] = v; sum += v; }
-    sum = warp_sum(sum);
-    __syncwarp();
-    for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
+    if (sigmoid_scores) {
+        for (int e = lane; e < E; e += 32) s[e] = sigmoid_exact(z[e]);
+    } else {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float v = expf(z[e] - m); s[e] = v; sum += v; }
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
+    }
     __syncwarp();
     const int per = E / groups;
     for (int g = lane; g < groups; g += 32) {
@@ -1128,6 +1146,12 @@ route_kernel(const float* __restrict__ proj, int ldp, int o_router, int E, int t
             if (bi < E) s[bi] = -1.f;
         }
         __syncwarp();
+    }
+    if (lane == 0 && (normalise || scale != 1.f)) {
+        float* w = wts + (size_t)t * top;
+        float total = 0.f;
+        for (int r = 0; r < top; ++r) total += w[r];
+        for (int r = 0; r < top; ++r) w[r] = (normalise ? w[r] / (total + 1e-20f) : w[r]) * scale;
     }
 }
 
@@ -1167,12 +1191,14 @@ route_sort_kernel(const int* __restrict__ ids, int n_pairs, int top, int E, int*
 }
 
 int launch_route(const float* proj, int ldp, int o_router, int E, int top, int groups, int keep, int* ids, float* wts,
-                 int* seg, int* slot_token, int* slot_pos, int T, cudaStream_t stream) {
+                 int* seg, int* slot_token, int* slot_pos, int T, cudaStream_t stream, int route_kind, int normalise,
+                 float scale) {
     FT_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups && top >= 1 && top <= (E / groups) * keep,
                "router: %d experts, %d groups, keep %d, top %d do not fit together", E, groups, keep, top);
     const size_t smem = (size_t)4 * (E + groups) * 4;
     FT_REQUIRE(smem <= 48 * 1024 && (size_t)(E + 1) * 4 <= 48 * 1024, "router: %d experts are too many", E);
-    route_kernel<<<(T + 3) / 4, 128, smem, stream>>>(proj, ldp, o_router, E, top, groups, keep, ids, wts, T);
+    route_kernel<<<(T + 3) / 4, 128, smem, stream>>>(proj, ldp, o_router, E, top, groups, keep, ids, wts, T,
+                                                     route_kind == FT_ROUTE_SIGMOID, normalise, scale > 0.f ? scale : 1.f);
     FT_CHECK_CUDA(cudaGetLastError());
     route_sort_kernel<<<1, 1024, (size_t)(E + 1) * 4, stream>>>(ids, T * top, top, E, seg, slot_token, slot_pos);
     FT_CHECK_CUDA(cudaGetLastError());

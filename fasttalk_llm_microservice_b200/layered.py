@@ -5,6 +5,12 @@ added through element-wise sigmoid gates), two token mixers — latent attention
 normed latent per token, and a gated delta rule with one decay per head and key channel, whose state lives in a
 per-session slot — a mixture of experts with group-limited routing, and tanh-capped logits.
 
+The second design is Gedelorn: sandwich layers (an RMS norm with a gain per coordinate before and after each sublayer, the
+weight stored as gain - 1), branch mixers — a gated matrix memory ("mlstm"), a selective state space ("mamba2"), and a
+"parallel" mixer that adds a sliding-window softmax attention (rotary pairs, capped scores, keys reused as values) to a
+linear attention with a constant decay per head — and a feed-forward that is either a dense SwiGLU or a mixture of
+squared-ReLU experts with sigmoid scores and a shared expert.  Its mixers are ft_branch_desc entries of the native engine.
+
 The reference names models by tag only and owns no model code (app/utils/config.py:86, docker-compose.vllm.yml:39); this
 module is the model side of what its engine container would load: config.json -> LayeredSpec, model.safetensors -> the
 tensors by their names in the file, pack() -> the device arrays and descriptors the native engine reads.
@@ -19,17 +25,46 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-MIXER_LATENT_ATTENTION, MIXER_CHANNEL_DELTA = 1, 2
-FF_NONE, FF_MOE = 0, 1
-MIXERS = {"latent_attention": MIXER_LATENT_ATTENTION, "channel_delta": MIXER_CHANNEL_DELTA}
+MIXER_LATENT_ATTENTION, MIXER_CHANNEL_DELTA, MIXER_BRANCHES = 1, 2, 3
+FF_NONE, FF_MOE, FF_DENSE = 0, 1, 2
+LAYER_GATED, LAYER_SANDWICH = 0, 1
+ACT_SWIGLU, ACT_RELU2 = 0, 1
+ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1
+BRANCH_WINDOW_ATTENTION, BRANCH_DECAY_ATTENTION, BRANCH_MATRIX_MEMORY, BRANCH_STATE_SPACE = 1, 2, 3, 4
+MIXERS = {"latent_attention": MIXER_LATENT_ATTENTION, "channel_delta": MIXER_CHANNEL_DELTA,
+          "mlstm": MIXER_BRANCHES, "mamba2": MIXER_BRANCHES, "parallel": MIXER_BRANCHES}
+BRANCHES = {"window_attention": BRANCH_WINDOW_ATTENTION, "decay_attention": BRANCH_DECAY_ATTENTION,
+            "matrix_memory": BRANCH_MATRIX_MEMORY, "state_space": BRANCH_STATE_SPACE}
+SANDWICH_MIXERS = ("mlstm", "mamba2", "parallel")
+
+
+@dataclass(frozen=True)
+class BranchSpec:
+    """One token mixer of a branch layer (ft_branch_desc).  `prefix` is where its tensors live below '<layer>.mix.'."""
+    kind: str                       # key of BRANCHES
+    heads: int
+    dim: int                        # query / key size per head (state space: the state size)
+    vdim: int
+    kv_heads: int = 0               # window attention: key heads; state space: groups; otherwise = heads
+    prefix: str = ""
+    out_scale: float = 1.0
+    scale: float = 1.0              # window attention
+    softcap: float = 0.0
+    window: int = 0
+    rot_dims: int = 0
+    rot_base: float = 10000.0
+    decay: Tuple[float, ...] = ()   # decay attention
+    gate_cap: float = 0.0           # matrix memory
+    conv: int = 0                   # state space
+    norm_groups: int = 1
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    mixer: str                      # "latent_attention" | "channel_delta"
-    heads: int
-    dim: int
-    vdim: int
+    mixer: str                      # "latent_attention" | "channel_delta" | "mlstm" | "mamba2" | "parallel"
+    heads: int = 0
+    dim: int = 0
+    vdim: int = 0
     kv_heads: int = 0               # channel_delta
     conv: int = 0                   # channel_delta: taps
     rank_a: int = 0                 # channel_delta: inner size of the decay projection (from the tensor's shape)
@@ -41,6 +76,12 @@ class LayerSpec:
     top: int = 0
     groups: int = 1
     keep: int = 1
+    # sandwich layers (Gedelorn)
+    form: str = "gated"             # "gated" | "sandwich"
+    branches: Tuple[BranchSpec, ...] = ()
+    ff_kind: str = ""               # sandwich: "" (none) | "dense" | "moe"
+    route_scale: float = 1.0
+    shared_ff: int = 0
 
 
 @dataclass(frozen=True)
@@ -62,6 +103,9 @@ class LayeredSpec:
         """The config.json of this spec."""
         out = []
         for l in self.layers:
+            if l.form == "sandwich":
+                out.append(_sandwich_layer_config(l))
+                continue
             if l.mixer == "latent_attention":
                 mixer = {"dim": l.dim, "heads": l.heads, "kv_rank": l.kv_rank, "scale": l.scale, "vdim": l.vdim}
             else:
@@ -71,8 +115,92 @@ class LayeredSpec:
                 mlp = {"expert": {"ff": l.ff}, "kind": "moe",
                        "router": {"experts": l.experts, "groups": {"count": l.groups, "keep": l.keep}, "top": l.top}}
             out.append({"mixer": mixer, "mlp": mlp, "type": l.mixer})
-        return {"architecture": self.architecture, "layers": out, "logit_softcap": self.logit_softcap,
-                "norm": {"eps": self.eps}, "vocab": self.vocab, "width": self.width}
+        cfg = {"architecture": self.architecture, "layers": out, "norm": {"eps": self.eps}, "vocab": self.vocab,
+               "width": self.width}
+        if self.logit_softcap or self.architecture == "Gitozen":
+            cfg["logit_softcap"] = self.logit_softcap
+        return cfg
+
+
+def _branch_config(b: BranchSpec) -> Dict:
+    if b.kind == "window_attention":
+        m = {"dim": b.dim, "heads": b.heads, "kv_heads": b.kv_heads, "mask": {"size": b.window}, "scale": b.scale,
+             "vdim": b.vdim}
+        if b.rot_dims:
+            m["rot"] = {"base": b.rot_base, "dims": b.rot_dims}
+        if b.softcap:
+            m["softcap"] = b.softcap
+        return m
+    if b.kind == "decay_attention":
+        return {"decay": list(b.decay), "dim": b.dim, "heads": b.heads, "vdim": b.vdim}
+    if b.kind == "matrix_memory":
+        return {"dim": b.dim, "gate_cap": b.gate_cap, "heads": b.heads, "vdim": b.vdim}
+    return {"conv": b.conv, "groups": b.kv_heads, "heads": b.heads, "norm_groups": b.norm_groups, "state": b.dim,
+            "vdim": b.vdim}
+
+
+def _sandwich_layer_config(l: LayerSpec) -> Dict:
+    if l.mixer == "parallel":
+        left, right = l.branches
+        mixer = {"left": _branch_config(left), "left_scale": left.out_scale, "right": _branch_config(right),
+                 "right_scale": right.out_scale}
+    else:
+        mixer = _branch_config(l.branches[0])
+    mlp = None
+    if l.ff_kind == "dense":
+        mlp = {"ff": l.ff, "kind": "dense"}
+    elif l.ff_kind == "moe":
+        mlp = {"expert": {"ff": l.ff}, "kind": "moe",
+               "router": {"experts": l.experts, "scale": l.route_scale, "top": l.top}}
+        if l.shared_ff:
+            mlp["shared"] = {"ff": l.shared_ff}
+    return {"mixer": mixer, "mlp": mlp, "type": l.mixer}
+
+
+def _branch_from_config(kind: str, m: Dict, prefix: str = "", out_scale: float = 1.0) -> BranchSpec:
+    if kind == "window_attention":
+        rot = m.get("rot") or {}
+        return BranchSpec(kind=kind, heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]),
+                          vdim=int(m.get("vdim", m["dim"])), prefix=prefix, out_scale=out_scale, scale=float(m["scale"]),
+                          softcap=float(m.get("softcap") or 0.0), window=int((m.get("mask") or {}).get("size", 0)),
+                          rot_dims=int(rot.get("dims", 0)), rot_base=float(rot.get("base", 10000.0)))
+    if kind == "decay_attention":
+        decay = tuple(float(x) for x in m["decay"])
+        if len(decay) != int(m["heads"]):
+            raise ValueError(f"{len(decay)} decays for {m['heads']} heads")
+        return BranchSpec(kind=kind, heads=int(m["heads"]), kv_heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                          prefix=prefix, out_scale=out_scale, decay=decay)
+    if kind == "matrix_memory":
+        return BranchSpec(kind=kind, heads=int(m["heads"]), kv_heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                          prefix=prefix, out_scale=out_scale, gate_cap=float(m["gate_cap"]))
+    if kind == "state_space":
+        return BranchSpec(kind=kind, heads=int(m["heads"]), kv_heads=int(m.get("groups", 1)), dim=int(m["state"]),
+                          vdim=int(m["vdim"]), prefix=prefix, out_scale=out_scale, conv=int(m["conv"]),
+                          norm_groups=int(m.get("norm_groups", 1)))
+    raise ValueError(f"unknown branch kind {kind!r}")
+
+
+def _sandwich_layer_from_config(i: int, l: Dict) -> LayerSpec:
+    kind, m = l["type"], l["mixer"]
+    if kind == "mlstm":
+        branches = (_branch_from_config("matrix_memory", m),)
+    elif kind == "mamba2":
+        branches = (_branch_from_config("state_space", m),)
+    else:
+        branches = (_branch_from_config("window_attention", m["left"], "left.", float(m.get("left_scale", 1.0))),
+                    _branch_from_config("decay_attention", m["right"], "right.", float(m.get("right_scale", 1.0))))
+    kw = dict(mixer=kind, form="sandwich", branches=branches)
+    mlp = l.get("mlp")
+    if mlp:
+        if mlp["kind"] == "dense":
+            kw.update(ff_kind="dense", ff=int(mlp["ff"]))
+        elif mlp["kind"] == "moe":
+            r = mlp["router"]
+            kw.update(ff_kind="moe", ff=int(mlp["expert"]["ff"]), experts=int(r["experts"]), top=int(r["top"]),
+                      route_scale=float(r.get("scale", 1.0)), shared_ff=int((mlp.get("shared") or {}).get("ff", 0)))
+        else:
+            raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+    return LayerSpec(**kw)
 
 
 def spec_from_config(cfg: Dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = None, name: str = "checkpoint") -> LayeredSpec:
@@ -82,6 +210,9 @@ def spec_from_config(cfg: Dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = N
         kind, m = l["type"], l["mixer"]
         if kind not in MIXERS:
             raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+        if kind in SANDWICH_MIXERS:
+            layers.append(_sandwich_layer_from_config(i, l))
+            continue
         kw = dict(mixer=kind, heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]))
         if kind == "latent_attention":
             kw.update(kv_rank=int(m["kv_rank"]), scale=float(m["scale"]))
@@ -112,6 +243,9 @@ def tensor_shapes(spec: LayeredSpec) -> Dict[str, Tuple[int, ...]]:
     out: Dict[str, Tuple[int, ...]] = {"embed": (spec.vocab, W)}
     for i, l in enumerate(spec.layers):
         p = f"l{i}."
+        if l.form == "sandwich":
+            out.update(_sandwich_shapes(p, l, W))
+            continue
         out[p + "norm1"] = ()
         if l.mixer == "latent_attention":
             out.update({p + "mix.q": (l.heads * l.dim, W), p + "mix.dkv": (l.kv_rank, W), p + "mix.dkv.norm": (l.kv_rank,),
@@ -131,8 +265,41 @@ def tensor_shapes(spec: LayeredSpec) -> Dict[str, Tuple[int, ...]]:
             out[p + "mlp.router"] = (l.experts, W)
             out.update({p + "rg2": (W, W), p + "rg2.b": (W,)})
         out.update({p + "rg1": (W, W), p + "rg1.b": (W,)})
-    out["final.norm"] = ()
+    out["final.norm"] = (W,) if spec.layers and spec.layers[-1].form == "sandwich" else ()
     out["head"] = (spec.vocab, W)
+    return out
+
+
+def _sandwich_shapes(p: str, l: LayerSpec, W: int) -> Dict[str, Tuple[int, ...]]:
+    out: Dict[str, Tuple[int, ...]] = {p + "norm1": (W,), p + "norm1b": (W,)}
+    for b in l.branches:
+        m = p + "mix." + b.prefix
+        hv = b.heads * b.vdim
+        if b.kind == "window_attention":
+            out.update({m + "q": (b.heads * b.dim, W), m + "q.b": (b.heads * b.dim,), m + "k": (b.kv_heads * b.dim, W),
+                        m + "k.b": (b.kv_heads * b.dim,), m + "o": (W, hv)})
+        elif b.kind == "decay_attention":
+            out.update({m + "q": (b.heads * b.dim, W), m + "k": (b.heads * b.dim, W), m + "v": (hv, W), m + "g": (hv, W),
+                        m + "o": (W, hv), m + "norm": (hv,)})
+        elif b.kind == "matrix_memory":
+            out.update({m + "q": (b.heads * b.dim, W), m + "k": (b.heads * b.dim, W), m + "v": (hv, W), m + "g": (hv, W),
+                        m + "o": (W, hv), m + "norm": (hv,), m + "i": (b.heads, W), m + "i.b": (b.heads,),
+                        m + "f": (b.heads, W), m + "f.b": (b.heads,)})
+        else:
+            ch = hv + 2 * b.kv_heads * b.dim
+            out.update({m + "in": (hv + ch + b.heads, W), m + "conv": (ch, b.conv), m + "conv.b": (ch,),
+                        m + "dt_bias": (b.heads,), m + "A_log": (b.heads,), m + "D": (b.heads,), m + "norm": (hv,),
+                        m + "o": (W, hv)})
+    if l.ff_kind:
+        out.update({p + "norm2": (W,), p + "norm2b": (W,)})
+    if l.ff_kind == "dense":
+        out.update({p + "mlp.gate": (l.ff, W), p + "mlp.up": (l.ff, W), p + "mlp.down": (W, l.ff)})
+    elif l.ff_kind == "moe":
+        for e in range(l.experts):
+            out.update({f"{p}mlp.e{e}.up": (l.ff, W), f"{p}mlp.e{e}.down": (W, l.ff)})
+        out[p + "mlp.router"] = (l.experts, W)
+        if l.shared_ff:
+            out.update({p + "mlp.shared.up": (l.shared_ff, W), p + "mlp.shared.down": (W, l.shared_ff)})
     return out
 
 
@@ -142,9 +309,18 @@ def init_weights(spec: LayeredSpec, seed: int = 0, device: str = "cpu") -> Dict[
     g = torch.Generator(device="cpu")
     g.manual_seed(seed)
     w = {}
+    sandwich = bool(spec.layers) and spec.layers[-1].form == "sandwich"
     for name, shape in tensor_shapes(spec).items():
         leaf = name.split(".")[-1]
-        if name.endswith("norm1") or name == "final.norm" or name.endswith(".norm"):
+        if sandwich and (leaf in ("norm1", "norm1b", "norm2", "norm2b") or name == "final.norm"):
+            t = 0.2 * torch.randn(shape, generator=g)          # stored as gain - 1
+        elif sandwich and leaf == "b":
+            t = 0.5 * torch.randn(shape, generator=g)
+            if name.endswith("f.b"):
+                t = t + 3.0                                      # forget gates that mostly keep
+        elif sandwich and leaf == "D":
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        elif name.endswith("norm1") or name == "final.norm" or name.endswith(".norm"):
             t = 1.0 + 0.1 * torch.randn(shape, generator=g)
         elif leaf == "A_log":
             t = torch.log(0.5 + 2.0 * torch.rand(shape, generator=g))
@@ -199,6 +375,23 @@ def save_checkpoint(spec: LayeredSpec, w: Dict[str, torch.Tensor], path: str) ->
 
 
 # ------------------------------------------------------------------ native side
+class BranchDesc(C.Structure):
+    """ft_branch_desc (include/fasttalk_b200.h)."""
+    _fields_ = [
+        ("kind", C.c_int), ("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int),
+        ("out_scale", C.c_float),
+        ("o_q", C.c_int), ("o_k", C.c_int), ("o_v", C.c_int), ("o_g", C.c_int), ("o_z", C.c_int), ("o_dt", C.c_int),
+        ("o_i", C.c_int), ("o_f", C.c_int),
+        ("w_o", C.c_void_p), ("out_norm", C.c_void_p),
+        ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int), ("rot_dims", C.c_int),
+        ("rot_freq", C.c_void_p), ("q_bias", C.c_void_p), ("k_bias", C.c_void_p),
+        ("decay", C.c_void_p),
+        ("gate_cap", C.c_float), ("gate_bias", C.c_void_p),
+        ("conv", C.c_int), ("norm_groups", C.c_int),
+        ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("dt_bias", C.c_void_p), ("a_log", C.c_void_p), ("skip", C.c_void_p),
+    ]
+
+
 class LayerDesc(C.Structure):
     """ft_layer_desc (include/fasttalk_b200.h)."""
     _fields_ = [
@@ -214,6 +407,10 @@ class LayerDesc(C.Structure):
         ("conv_w", C.c_void_p), ("w_a2", C.c_void_p), ("w_g2", C.c_void_p), ("dt_bias", C.c_void_p),
         ("a_log", C.c_void_p), ("out_norm", C.c_void_p),
         ("w_gu", C.c_void_p), ("w_down", C.c_void_p),
+        ("form", C.c_int), ("n_branches", C.c_int), ("branch", BranchDesc * 2),
+        ("norm_pre1", C.c_void_p), ("norm_post1", C.c_void_p), ("norm_pre2", C.c_void_p), ("norm_post2", C.c_void_p),
+        ("ff_act", C.c_int), ("route_kind", C.c_int), ("route_norm", C.c_int), ("route_scale", C.c_float),
+        ("w_router", C.c_void_p), ("shared_ff", C.c_int), ("w_shared_up", C.c_void_p), ("w_shared_down", C.c_void_p),
     ]
 
 
@@ -223,6 +420,7 @@ class LayeredModel(C.Structure):
         ("width", C.c_int), ("vocab", C.c_int), ("n_layers", C.c_int),
         ("eps", C.c_float), ("logit_softcap", C.c_float), ("final_norm_gain", C.c_float),
         ("embed", C.c_void_p), ("head", C.c_void_p), ("layers", C.POINTER(LayerDesc)), ("exact_f32", C.c_int),
+        ("final_norm_w", C.c_void_p),
     ]
 
 
@@ -242,6 +440,100 @@ def _stack_inputs(parts: List[Tuple[str, torch.Tensor]], width: int, device) -> 
     return out, offs
 
 
+def _interleave(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Rows (2j, 2j+1) = (a_j, b_j): the paired layout the SwiGLU epilogue reads."""
+    out = torch.empty(2 * a.shape[0], a.shape[1], dtype=a.dtype, device=a.device)
+    out[0::2], out[1::2] = a, b
+    return out
+
+
+def _pack_sandwich_layer(l: LayerSpec, w: Dict[str, torch.Tensor], p: str, d, W: int, device, dev, keep: list) -> None:
+    """Descriptor of a sandwich layer: its branches' projections stacked into w_in, norm gains as 1 + stored weight."""
+    f32 = torch.float32
+    d.form, d.mixer, d.n_branches = LAYER_SANDWICH, MIXER_BRANCHES, len(l.branches)
+    for f_ in ("o_q", "o_k", "o_v", "o_dkv", "o_gate", "o_beta", "o_a1", "o_g1", "o_rg1", "o_rg2", "o_router"):
+        setattr(d, f_, -1)
+    d.norm_gain = 1.0
+    gain = lambda name: dev(1.0 + w[name].float(), f32).data_ptr()
+    d.norm_pre1, d.norm_post1 = gain(p + "norm1"), gain(p + "norm1b")
+    parts: List[Tuple[str, torch.Tensor]] = []
+    for k, b in enumerate(l.branches):
+        m = p + "mix." + b.prefix
+        if b.kind == "window_attention":
+            parts += [(f"{k}q", w[m + "q"]), (f"{k}k", w[m + "k"])]
+        elif b.kind == "decay_attention":      # q | k | v adjacent: one SiLU pass covers them
+            parts += [(f"{k}q", torch.cat([w[m + "q"], w[m + "k"], w[m + "v"]], 0)), (f"{k}g", w[m + "g"])]
+        elif b.kind == "matrix_memory":
+            parts += [(f"{k}q", w[m + "q"]), (f"{k}k", w[m + "k"]), (f"{k}v", w[m + "v"]), (f"{k}g", w[m + "g"]),
+                      (f"{k}i", w[m + "i"]), (f"{k}f", w[m + "f"])]
+        else:                                   # z | x | B | C | dt as the checkpoint stores them
+            parts += [(f"{k}z", w[m + "in"])]
+    w_in, offs = _stack_inputs([(n, t.to(device)) for n, t in parts], W, device)
+    keep.append(w_in)
+    d.w_in, d.n_in = w_in.data_ptr(), w_in.shape[0]
+    for k, b in enumerate(l.branches):
+        m = p + "mix." + b.prefix
+        c = d.branch[k]
+        c.kind, c.heads, c.kv_heads, c.dim, c.vdim = BRANCHES[b.kind], b.heads, b.kv_heads or b.heads, b.dim, b.vdim
+        c.out_scale = b.out_scale
+        for f_ in ("o_q", "o_k", "o_v", "o_g", "o_z", "o_dt", "o_i", "o_f"):
+            setattr(c, f_, -1)
+        c.w_o = dev(w[m + "o"]).data_ptr()
+        hv = b.heads * b.vdim
+        if b.kind == "window_attention":
+            c.o_q, c.o_k = offs[f"{k}q"], offs[f"{k}k"]
+            c.scale, c.softcap, c.window, c.rot_dims = b.scale, b.softcap, b.window, b.rot_dims
+            if b.rot_dims:
+                i2 = torch.arange(b.rot_dims // 2, dtype=torch.float64)
+                c.rot_freq = dev(torch.tensor(b.rot_base, dtype=torch.float64) ** (-2.0 * i2 / b.rot_dims), f32).data_ptr()
+            if m + "q.b" in w:
+                c.q_bias, c.k_bias = dev(w[m + "q.b"], f32).data_ptr(), dev(w[m + "k.b"], f32).data_ptr()
+        elif b.kind == "decay_attention":
+            c.o_q = offs[f"{k}q"]
+            c.o_k = c.o_q + b.heads * b.dim
+            c.o_v = c.o_k + b.heads * b.dim
+            c.o_g = offs[f"{k}g"]
+            c.decay = dev(torch.tensor(b.decay, dtype=torch.float64), f32).data_ptr()
+            c.out_norm = dev(w[m + "norm"], f32).data_ptr()
+        elif b.kind == "matrix_memory":
+            c.o_q, c.o_k, c.o_v, c.o_g, c.o_i, c.o_f = (offs[f"{k}{x}"] for x in "qkvgif")
+            c.gate_cap = b.gate_cap
+            c.gate_bias = dev(torch.cat([w[m + "i.b"].float().cpu(), w[m + "f.b"].float().cpu()]), f32).data_ptr()
+            c.out_norm = dev(w[m + "norm"], f32).data_ptr()
+        else:
+            gn = c.kv_heads * b.dim
+            c.o_z = offs[f"{k}z"]
+            c.o_v = c.o_z + hv
+            c.o_k = c.o_v + hv
+            c.o_q = c.o_k + gn
+            c.o_dt = c.o_q + gn
+            c.conv, c.norm_groups = b.conv, b.norm_groups
+            c.conv_w = dev(w[m + "conv"], f32).data_ptr()
+            c.conv_b = dev(w[m + "conv.b"], f32).data_ptr()
+            c.dt_bias = dev(w[m + "dt_bias"], f32).data_ptr()
+            c.a_log = dev(w[m + "A_log"], f32).data_ptr()
+            c.skip = dev(w[m + "D"], f32).data_ptr()
+            c.out_norm = dev(w[m + "norm"], f32).data_ptr()
+    d.ff_kind = FF_NONE
+    if l.ff_kind:
+        d.norm_pre2, d.norm_post2 = gain(p + "norm2"), gain(p + "norm2b")
+        d.ff = l.ff
+    if l.ff_kind == "dense":
+        d.ff_kind, d.ff_act = FF_DENSE, ACT_SWIGLU
+        d.w_gu = dev(_interleave(w[p + "mlp.gate"].to(device), w[p + "mlp.up"].to(device))).data_ptr()
+        d.w_down = dev(w[p + "mlp.down"]).data_ptr()
+    elif l.ff_kind == "moe":
+        d.ff_kind, d.ff_act, d.experts, d.top, d.groups, d.keep = FF_MOE, ACT_RELU2, l.experts, l.top, 1, 1
+        d.route_kind, d.route_norm, d.route_scale = ROUTE_SIGMOID, 1, l.route_scale
+        d.w_router = dev(w[p + "mlp.router"]).data_ptr()
+        d.w_gu = dev(torch.stack([w[f"{p}mlp.e{e}.up"].to(device) for e in range(l.experts)])).data_ptr()
+        d.w_down = dev(torch.stack([w[f"{p}mlp.e{e}.down"].to(device) for e in range(l.experts)])).data_ptr()
+        if l.shared_ff:
+            d.shared_ff = l.shared_ff
+            d.w_shared_up = dev(w[p + "mlp.shared.up"]).data_ptr()
+            d.w_shared_down = dev(w[p + "mlp.shared.down"]).data_ptr()
+
+
 def pack(spec: LayeredSpec, w: Dict[str, torch.Tensor], device, exact_f32: bool = False) -> Tuple[LayeredModel, list]:
     """Device arrays in the engine's layout + the descriptor structs.  Returns (model, keepalive): the engine borrows
     the pointers, so `keepalive` has to live as long as the engine."""
@@ -258,6 +550,9 @@ def pack(spec: LayeredSpec, w: Dict[str, torch.Tensor], device, exact_f32: bool 
     for i, l in enumerate(spec.layers):
         p, d = f"l{i}.", descs[i]
         m = p + "mix."
+        if l.form == "sandwich":
+            _pack_sandwich_layer(l, w, p, d, W, device, dev, keep)
+            continue
         d.mixer, d.heads, d.dim, d.vdim = MIXERS[l.mixer], l.heads, l.dim, l.vdim
         d.norm_gain = float(w[p + "norm1"].float().item())
         for f_ in ("o_q", "o_k", "o_v", "o_dkv", "o_gate", "o_beta", "o_a1", "o_g1", "o_rg1", "o_rg2", "o_router"):
@@ -311,7 +606,11 @@ def pack(spec: LayeredSpec, w: Dict[str, torch.Tensor], device, exact_f32: bool 
     model = LayeredModel()
     model.width, model.vocab, model.n_layers = W, spec.vocab, len(spec.layers)
     model.eps, model.logit_softcap = spec.eps, spec.logit_softcap
-    model.final_norm_gain = float(w["final.norm"].float().item())
+    if w["final.norm"].dim() == 0:
+        model.final_norm_gain = float(w["final.norm"].float().item())
+    else:
+        model.final_norm_gain = 1.0
+        model.final_norm_w = dev(1.0 + w["final.norm"].float(), torch.float32).data_ptr()
     model.embed = dev(w["embed"]).data_ptr()
     model.head = dev(w["head"]).data_ptr()
     model.layers = C.cast(descs, C.POINTER(LayerDesc))

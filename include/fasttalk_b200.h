@@ -185,8 +185,62 @@ int ft_debug_prefill_logits(ft_engine* e, const int* tokens, int n_tokens, int c
  * columns are addressed by the o_* offsets (-1 = the layer has no such part).
  * Small vectors are fp32 device arrays; matrices are bf16 [out, in] row-major.
  * ---------------------------------------------------------------------------------------- */
-enum { FT_MIXER_LATENT_ATTENTION = 1, FT_MIXER_CHANNEL_DELTA = 2 };
-enum { FT_FF_NONE = 0, FT_FF_MOE = 1 };
+enum { FT_MIXER_LATENT_ATTENTION = 1, FT_MIXER_CHANNEL_DELTA = 2, FT_MIXER_BRANCHES = 3 };
+enum { FT_FF_NONE = 0, FT_FF_MOE = 1, FT_FF_DENSE = 2 };
+/* How a layer joins its sublayers to the stream.
+ *   FT_LAYER_GATED:    the form above (one scalar-gain norm feeds both sublayers, sigmoid gates on the way back).
+ *   FT_LAYER_SANDWICH: x += post1(mixer(pre1(x))); x += post2(ff(pre2(x))), each of the four an RMS norm with a gain per
+ *                      coordinate, given as the gain itself (a checkpoint that stores gain - 1 is converted at load time). */
+enum { FT_LAYER_GATED = 0, FT_LAYER_SANDWICH = 1 };
+enum { FT_ACT_SWIGLU = 0, FT_ACT_RELU2 = 1 };          /* expert: W_down (silu(W_gate h) * W_up h)  |  W_down relu(W_up h)^2 */
+enum { FT_ROUTE_SOFTMAX = 0, FT_ROUTE_SIGMOID = 1 };   /* router scores over all experts */
+
+/* Branch mixers (mixer == FT_MIXER_BRANCHES): one or two token mixers side by side on the same normed input, each with
+ * its own output projection; the mixer's result is sum_b out_scale_b * W_o_b branch_b(h).  The parts of a branch are
+ * columns of the layer's stacked input projection (o_* offsets, -1 = the branch has no such part).
+ *   FT_BRANCH_WINDOW_ATTENTION  grouped-query softmax attention over the last `window` positions (0 = all), rotary pairs
+ *                               (2i, 2i+1) on the first rot_dims coordinates, score = cap(q.k * scale); without o_v the
+ *                               values are the keys as projected (before rotation).  Paged cache: rotated keys and values.
+ *   the other three are linear recurrences over a matrix state S [dim][vdim] per head, kept in the session's state slot:
+ *       S <- a_t S + b_t k_t v_t^T,   o_t = S^T q_t          (a_t, b_t scalars per head and token, all in fp32)
+ *   FT_BRANCH_DECAY_ATTENTION   q, k, v = silu(projections); a = decay[head] (a constant), b = 1; the concatenated heads are
+ *                               RMS-normed together (gain out_norm), gated by sigmoid(g).
+ *   FT_BRANCH_MATRIX_MEMORY     q scaled by dim^-1/2; log gates i = cap tanh(.. / cap), f = logsigmoid(cap tanh(.. / cap)),
+ *                               running maximum m (starts at 0): a = exp(f + m' - m), b = exp(i - m); a normaliser vector n
+ *                               follows the same recurrence with k alone; o / (max(|n.q|, exp(-m)) + 1e-6); every head is
+ *                               divided by its own root mean square, then gain out_norm and the gate sigmoid(g).
+ *   FT_BRANCH_STATE_SPACE       x | B | C pass a short causal convolution (with bias) and SiLU; dt = softplus(dt + dt_bias);
+ *                               a = exp(-exp(a_log) dt), b = dt, k = B, q = C (kv_heads groups of heads share them), v = x;
+ *                               o += skip[head] * x; o *= silu(z); RMS norm in norm_groups equal parts, gain out_norm. */
+enum { FT_BRANCH_WINDOW_ATTENTION = 1, FT_BRANCH_DECAY_ATTENTION = 2, FT_BRANCH_MATRIX_MEMORY = 3, FT_BRANCH_STATE_SPACE = 4 };
+typedef struct {
+    int kind;                  /* FT_BRANCH_* */
+    int heads, kv_heads;       /* head h reads key (value) head h / (heads / kv_heads); state space: kv_heads = groups */
+    int dim, vdim;             /* per head: query/key size (state space: the state size N), value size */
+    float out_scale;
+    int o_q, o_k, o_v, o_g, o_z, o_dt, o_i, o_f;
+    const void* w_o;           /* bf16 [width, heads * vdim] */
+    const float* out_norm;     /* fp32 [heads * vdim] (null: window attention) */
+    /* window attention */
+    float scale, softcap;      /* softcap 0 = none */
+    int window, rot_dims;      /* window 0 = every earlier position; rot_dims 0 = no rotation */
+    const float* rot_freq;     /* fp32 [rot_dims / 2]: angle of pair i at position p = p * rot_freq[i] */
+    const float* q_bias;       /* fp32 [heads * dim] or null */
+    const float* k_bias;       /* fp32 [kv_heads * dim] or null */
+    /* decay attention */
+    const float* decay;        /* fp32 [heads] */
+    /* matrix memory */
+    float gate_cap;
+    const float* gate_bias;    /* fp32 [2 * heads]: input gates | forget gates */
+    /* state space */
+    int conv, norm_groups;
+    const float* conv_w;       /* fp32 [heads * vdim + 2 * kv_heads * dim][conv], rows x | B | C, last column = current token */
+    const float* conv_b;       /* fp32, one per channel */
+    const float* dt_bias;      /* fp32 [heads] */
+    const float* a_log;        /* fp32 [heads] */
+    const float* skip;         /* fp32 [heads] */
+} ft_branch_desc;
+
 typedef struct {
     int mixer;                 /* FT_MIXER_* */
     int heads, kv_heads;       /* channel delta: q / k have kv_heads heads, head h reads q/k head h / (heads / kv_heads) */
@@ -215,8 +269,27 @@ typedef struct {
     const float* a_log;        /* fp32 [heads] */
     const float* out_norm;     /* fp32 [vdim] */
     /* mixture of experts */
-    const void* w_gu;          /* bf16 [experts][2 * ff][width], rows (2j, 2j+1) = (gate_j, up_j) */
+    const void* w_gu;          /* bf16 [experts][2 * ff][width], rows (2j, 2j+1) = (gate_j, up_j); FT_ACT_RELU2: [experts][ff][width] */
     const void* w_down;        /* bf16 [experts][width][ff] */
+    /* ---- what the sandwich form and the branch mixers add (all zero for a gated layer of the first two mixers) ---- */
+    int form;                  /* FT_LAYER_* */
+    int n_branches;            /* mixer == FT_MIXER_BRANCHES: 1 or 2 */
+    ft_branch_desc branch[2];
+    const float* norm_pre1;    /* fp32 [width] gains of the four norms of a sandwich layer (pre2 / post2: null without feed-forward) */
+    const float* norm_post1;
+    const float* norm_pre2;
+    const float* norm_post2;
+    /* feed-forward of a sandwich layer reads its own normed input, so its projections are not part of w_in:
+     *   FT_FF_DENSE: w_gu [2 * ff][width] (paired rows), w_down [width][ff]
+     *   FT_FF_MOE:   w_router, experts in w_gu / w_down with activation ff_act, an optional shared expert for every token */
+    int ff_act;                /* FT_ACT_* of the experts and the shared expert */
+    int route_kind;            /* FT_ROUTE_* */
+    int route_norm;            /* 1: the chosen scores are divided by their sum (+ 1e-20) */
+    float route_scale;         /* then multiplied by this (0 = 1) */
+    const void* w_router;      /* bf16 [experts][width] */
+    int shared_ff;             /* 0 = no shared expert */
+    const void* w_shared_up;   /* bf16 [shared_ff (x 2, paired, for FT_ACT_SWIGLU)][width] */
+    const void* w_shared_down; /* bf16 [width][shared_ff] */
 } ft_layer_desc;
 
 typedef struct {
@@ -231,6 +304,7 @@ typedef struct {
                                   of more than a few rows whose shapes tile (rows of W a multiple of 128, columns of 64) run on
                                   the tensor cores (tcgen05) from bf16 hi + lo planes of the fp32 activations with fp32
                                   accumulation; norms, scores, softmax, router, recurrence and residual stay fp32 */
+    const float* final_norm_w; /* fp32 [width] or null: a gain per coordinate instead of final_norm_gain */
 } ft_layered_model;
 
 /* cfg: vocab, max_batch, max_batched_tokens, num_pages, max_context, max_sessions (= state slots), eos, debug_logit_rows
