@@ -207,3 +207,13 @@ def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
         if trail is not None:
             trail.append(x.clone())
     return offset_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def greedy(cfg: Dict, w: Dict[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+    """n tokens of argmax decoding, each from a full forward pass over everything so far."""
+    toks, out = list(prompt), []
+    for _ in range(n):
+        t = int(forward(cfg, w, toks)[-1].argmax())
+        out.append(t)
+        toks.append(t)
+    return out
