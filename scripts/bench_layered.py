@@ -1,9 +1,11 @@
-"""Prefill and decode throughput of the layered family (Gitozen) beside the closest Llama of equal size, random weights.
+"""Prefill and decode throughput of the layered family beside its closest relatives of equal size, random weights.
 
-    python bench.py --design gitozen [--sizes s,m] [--steps K] [--warmup W]
+    python bench.py --design gitozen  [--sizes s,m] [--arms gitozen,llama] [--steps K] [--warmup W]
+    python bench.py --design gedelorn [--sizes s,m] [--arms gedelorn,gitozen,llama] [--steps K] [--warmup W]
 
-For every size both models get the same width, depth, heads x head size, active feed-forward width (top x expert ff =
-Llama's ffn) and vocabulary.  Each arm is driven through Engine.feed (ft_engine_feed: the engine's own batch builder and
+For every size all arms get the same width, depth, heads x head size, active feed-forward width (top x expert ff =
+Llama's ffn) and vocabulary.  Gedelorn's closest relative in the framework is Gitozen (the same engine path: stacked
+input projection, a mixer with paged cache or state slot, experts, one residual-and-norm kernel per joint).  Each arm is driven through Engine.feed (ft_engine_feed: the engine's own batch builder and
 forward pass, nothing sampled), timed with CUDA events on the engine's stream; a 512 MB write between timed steps
 flushes L2.
   prefill  one fresh session, PREFILL tokens in one step
@@ -44,6 +46,26 @@ def gitozen_spec(name, c):
                                     conv=4, rank_a=64, rank_g=64, **moe))
     return LayeredSpec(name=f"gitozen-{name}", architecture="Gitozen", width=c["width"], vocab=c["vocab"], eps=1e-6,
                        logit_softcap=30.0, layers=tuple(layers))
+
+
+def gedelorn_spec(name, c):
+    """Four layers: state space + dense, parallel (window attention 512 | decay attention) + experts, matrix memory + dense,
+    state space + experts.  Heads x head size as in the other arms; the state space has the usual expansion of two."""
+    from fasttalk_llm_microservice_b200.layered import spec_from_config
+    W, H, D = c["width"], c["heads"], c["dim"]
+    space = {"type": "mamba2", "mixer": {"conv": 4, "groups": 1, "heads": 2 * W // 64, "norm_groups": 1, "state": 128, "vdim": 64}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"dim": D, "heads": H, "kv_heads": max(1, H // 4), "mask": {"size": 512}, "rot": {"base": 1e6, "dims": D},
+                 "scale": D ** -0.5, "softcap": 50.0, "vdim": D},
+        "left_scale": 1.0, "right": {"decay": [1.0 - 2.0 ** -(3 + 7 * h / max(1, H - 1)) for h in range(H)], "dim": D, "heads": H,
+                                     "vdim": D}, "right_scale": 1.0}}
+    mem = {"type": "mlstm", "mixer": {"dim": D, "gate_cap": 15.0, "heads": max(1, H // 2), "vdim": 2 * D}}
+    dense = {"ff": c["top"] * c["ff"], "kind": "dense"}
+    moe = {"expert": {"ff": c["ff"]}, "kind": "moe", "router": {"experts": c["experts"], "scale": 1.0, "top": c["top"]},
+           "shared": {"ff": c["ff"]}}
+    layers = [{**space, "mlp": dense}, {**par, "mlp": moe}, {**mem, "mlp": dense}, {**space, "mlp": moe}]
+    cfg = {"architecture": "Gedelorn", "layers": layers, "norm": {"eps": 1e-6}, "vocab": c["vocab"], "width": W}
+    return spec_from_config(cfg, name=f"gedelorn-{name}")
 
 
 def llama_spec(name, c):
@@ -107,9 +129,10 @@ def run(args) -> None:
     for name in only:
         c = SIZES[name]
         row = {"config": c}
-        for arm in (getattr(args, "arms", "") or "gitozen,llama").split(","):
-            if arm == "gitozen":
-                spec = gitozen_spec(name, c)
+        design = getattr(args, "design", "") or "gitozen"
+        for arm in (getattr(args, "arms", "") or ("gedelorn,gitozen,llama" if design == "gedelorn" else "gitozen,llama")).split(","):
+            if arm in ("gitozen", "gedelorn"):
+                spec = gitozen_spec(name, c) if arm == "gitozen" else gedelorn_spec(name, c)
                 w = init_layered(spec, seed=0, device="cuda")
             else:
                 spec = llama_spec(name, c)
@@ -121,7 +144,8 @@ def run(args) -> None:
             del eng, w
             torch.cuda.empty_cache()
         sizes[name] = row
-    print(json.dumps({"metric": "prefill / decode tok/s, Gitozen beside the closest Llama of equal size", "design": "gitozen",
-                      "dtype": "bf16 weights; Gitozen: fp32 activations, bf16 hi+lo planes on the tensor-core projections",
+    print(json.dumps({"metric": "prefill / decode tok/s of a layered design beside its closest relatives of equal size",
+                      "design": getattr(args, "design", "") or "gitozen",
+                      "dtype": "bf16 weights; layered family: fp32 activations, bf16 hi+lo planes on the tensor-core projections",
                       "data": "synthetic (random-init weights, random tokens)", "steps": steps, "warmup": warmup,
                       "l2": "512 MB write between timed steps", "sizes": sizes}), flush=True)
