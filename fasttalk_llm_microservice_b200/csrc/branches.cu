@@ -13,7 +13,7 @@
 //                        on it; they differ in how a, b, q, k, v are prepared and in the read-out that follows
 //   preparation          SiLU in place; gate pre-activations and the running-maximum scan of the matrix memory; short causal
 //                        convolution over a step's rows and the slot's tail, step sizes and decays of the state space
-//   read-out             normaliser, skip, gates and group-wise RMS norm in one pass per (token, norm group)
+//   read-out             normaliser, skip, gates and group-wise RMS norm, one CTA per (token, norm group)
 #include "common.cuh"
 #include "ft_internal.h"
 
@@ -247,18 +247,20 @@ int launch_window_attention(const WindowArgs& a, int T, cudaStream_t stream) {
 }
 
 // ------------------------------------------------------------------ scalar-decay rule
-// Lanes s = 0..LPC-1 of a column hold channels s * DPT .. s * DPT + DPT - 1 of that column of S.  A chunk of RCH tokens is
-// staged in shared memory (keys and queries padded with zeros to LPC * DPT channels, each lane's run 4 floats apart from
-// the next so that the 16-byte reads of the LPC runs fall into different banks), then the tokens are taken in order.
+// Lanes s = 0..LPC-1 of a column hold channels s * DPT .. s * DPT + DPT - 1 of that column of S.  Chunks of RCH tokens are
+// staged in shared memory one chunk ahead with asynchronous copies (keys and queries padded with zeros to LPC * DPT
+// channels, each lane's run 4 floats apart from the next so that the 16-byte reads of the LPC runs fall into different
+// banks), then the tokens of a chunk are taken in order.  The state is the only dependence from token to token; the
+// read-out o_t = S^T q_t (partial sums over a lane's run, then a shuffle tree over the LPC lanes) overlaps the next update.
 constexpr int RCH = 8, RTHREADS = 128;
+__device__ __forceinline__ void cp_async_f32(float* dst_smem, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
 template <int LPC, int DPT>
 __global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
     constexpr int VB = RTHREADS / LPC, RUN = DPT + 4, DP = LPC * RUN;
+    constexpr int BUF = 2 * RCH * DP + RCH * VB + RCH * 2;      // floats of one staged chunk: keys | queries | values | (a, b)
     extern __shared__ __align__(16) float rs[];
-    float* sk = rs;                        // [RCH][DP]
-    float* sqq = sk + RCH * DP;            // [RCH][DP]
-    float* sv = sqq + RCH * DP;            // [RCH][VB]
-    float* sab = sv + RCH * VB;            // [RCH][2]
     const int r = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * VB;
     const int s = threadIdx.x % LPC, jl = threadIdx.x / LPC, j = j0 + jl;
     const int t0 = a.req_start[r], t1 = a.req_start[r + 1];
@@ -266,52 +268,76 @@ __global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
     const int gh = h / (a.heads / a.qk_heads);
     float* S = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.s_off + (size_t)h * a.dim * a.vd;
     const bool live = j < a.vd;
+    for (int i = threadIdx.x; i < 2 * BUF; i += RTHREADS) rs[i] = 0.f;      // the padding stays zero from here on
     float st[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = s * DPT + i;
         st[i] = (a.req_pos0[r] > 0 && live && d < a.dim) ? S[(size_t)d * a.vd + j] : 0.f;
     }
-    for (int c0 = t0; c0 < t1; c0 += RCH) {
+    __syncthreads();
+    auto stage = [&](int buf, int c0) {
+        float* sk = rs + buf * BUF;
+        float* sq = sk + RCH * DP;
+        float* sv = sq + RCH * DP;
+        float* sab = sv + RCH * VB;
         const int nt = min(RCH, t1 - c0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < nt * LPC * DPT; i += RTHREADS) {
-            const int tt = i / (LPC * DPT), d = i % (LPC * DPT);
+        for (int i = threadIdx.x; i < nt * a.dim; i += RTHREADS) {
+            const int tt = i / a.dim, d = i - tt * a.dim;
             const int at = tt * DP + (d / DPT) * RUN + (d % DPT);
-            const bool in = d < a.dim;
-            sk[at] = in ? a.k[(size_t)(c0 + tt) * a.ldk + (size_t)gh * a.dim + d] : 0.f;
-            sqq[at] = in ? a.q[(size_t)(c0 + tt) * a.ldq + (size_t)gh * a.dim + d] : 0.f;
+            cp_async_f32(sk + at, a.k + (size_t)(c0 + tt) * a.ldk + (size_t)gh * a.dim + d);
+            cp_async_f32(sq + at, a.q + (size_t)(c0 + tt) * a.ldq + (size_t)gh * a.dim + d);
         }
         for (int i = threadIdx.x; i < nt * VB; i += RTHREADS) {
             const int tt = i / VB, c = i % VB;
-            sv[i] = j0 + c < a.vd ? a.v[(size_t)(c0 + tt) * a.ldv + (size_t)h * a.vd + j0 + c] : 0.f;
+            if (j0 + c < a.vd) cp_async_f32(sv + i, a.v + (size_t)(c0 + tt) * a.ldv + (size_t)h * a.vd + j0 + c);
         }
         for (int i = threadIdx.x; i < nt * 2; i += RTHREADS)
-            sab[i] = a.ab[((size_t)(c0 + i / 2) * a.heads + h) * 2 + (i & 1)];
-        __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float da = sab[2 * tt], bv = sab[2 * tt + 1] * sv[tt * VB + jl];
-            const float* kp = sk + tt * DP + s * RUN;
-            const float* qp = sqq + tt * DP + s * RUN;
-            float o0 = 0.f, o1 = 0.f;
-#pragma unroll
-            for (int i = 0; i < DPT; i += 4) {
-                const float4 kv = *reinterpret_cast<const float4*>(kp + i);
-                const float4 qv = *reinterpret_cast<const float4*>(qp + i);
-                st[i] = fmaf(da, st[i], bv * kv.x);
-                st[i + 1] = fmaf(da, st[i + 1], bv * kv.y);
-                st[i + 2] = fmaf(da, st[i + 2], bv * kv.z);
-                st[i + 3] = fmaf(da, st[i + 3], bv * kv.w);
-                o0 = fmaf(st[i], qv.x, o0);
-                o1 = fmaf(st[i + 1], qv.y, o1);
-                o0 = fmaf(st[i + 2], qv.z, o0);
-                o1 = fmaf(st[i + 3], qv.w, o1);
-            }
-            float o = o0 + o1;
-#pragma unroll
-            for (int off = LPC / 2; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-            if (s == 0 && live) a.o[(size_t)(c0 + tt) * a.ldo + (size_t)h * a.vd + j] = o;
+            cp_async_f32(sab + i, a.ab + ((size_t)(c0 + i / 2) * a.heads + h) * 2 + (i & 1));
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, t0);
+    int buf = 0;
+    for (int c0 = t0; c0 < t1; c0 += RCH, buf ^= 1) {
+        const int nt = min(RCH, t1 - c0);
+        if (c0 + RCH < t1) {
+            stage(buf ^ 1, c0 + RCH);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
+        __syncthreads();
+        const float* sk = rs + buf * BUF;
+        const float* sq = sk + RCH * DP;
+        const float* sv = sq + RCH * DP;
+        const float* sab = sv + RCH * VB;
+#pragma unroll
+        for (int tt = 0; tt < RCH; ++tt) {
+            if (tt < nt) {
+                const float da = sab[2 * tt], bv = sab[2 * tt + 1] * sv[tt * VB + jl];
+                const float* kp = sk + tt * DP + s * RUN;
+                const float* qp = sq + tt * DP + s * RUN;
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT; i += 4) {
+                    const float4 kv = *reinterpret_cast<const float4*>(kp + i);
+                    const float4 qv = *reinterpret_cast<const float4*>(qp + i);
+                    st[i] = fmaf(da, st[i], bv * kv.x);
+                    st[i + 1] = fmaf(da, st[i + 1], bv * kv.y);
+                    st[i + 2] = fmaf(da, st[i + 2], bv * kv.z);
+                    st[i + 3] = fmaf(da, st[i + 3], bv * kv.w);
+                    o0 = fmaf(st[i], qv.x, o0);
+                    o1 = fmaf(st[i + 1], qv.y, o1);
+                    o2 = fmaf(st[i + 2], qv.z, o2);
+                    o3 = fmaf(st[i + 3], qv.w, o3);
+                }
+                float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+                for (int off = LPC / 2; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+                if (s == 0 && live) a.o[(size_t)(c0 + tt) * a.ldo + (size_t)h * a.vd + j] = o;
+            }
+        }
+        __syncthreads();
     }
     if (live) {
 #pragma unroll
@@ -325,7 +351,7 @@ __global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
 template <int LPC, int DPT>
 static int launch_decay_rule_t(const RecurArgs& a, int n_req, cudaStream_t stream) {
     constexpr int VB = RTHREADS / LPC, DP = LPC * (DPT + 4);
-    const size_t smem = (size_t)(2 * RCH * DP + RCH * VB + RCH * 2) * 4;
+    const size_t smem = (size_t)2 * (2 * RCH * DP + RCH * VB + RCH * 2) * 4;
     if (smem > 48 * 1024)
         FT_CHECK_CUDA(cudaFuncSetAttribute(decay_rule_kernel<LPC, DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((a.vd + VB - 1) / VB, a.heads, n_req);
@@ -334,17 +360,26 @@ static int launch_decay_rule_t(const RecurArgs& a, int n_req, cudaStream_t strea
     return 0;
 }
 
+// Lanes per column and channels per lane: the fewest lanes whose runs (<= 32 channels) cover dim — the widest column
+// blocks and the best-coalesced state traffic, what a step of many requests wants — and more lanes with shorter runs while
+// the grid would leave most of the GPU idle (one long prompt).  The split changes the order of a sum, nothing else.
 int launch_decay_rule(const RecurArgs& a, int n_req, cudaStream_t stream) {
     FT_REQUIRE(a.heads >= 1 && a.qk_heads >= 1 && a.heads % a.qk_heads == 0 && a.dim >= 1 && a.dim <= 1024 && a.vd >= 1,
                "decay rule: bad sizes (heads %d, key heads %d, dim %d, values %d)", a.heads, a.qk_heads, a.dim, a.vd);
     if (n_req <= 0) return 0;
-    if (a.dim <= 16) return launch_decay_rule_t<4, 4>(a, n_req, stream);
-    if (a.dim <= 32) return launch_decay_rule_t<4, 8>(a, n_req, stream);
-    if (a.dim <= 64) return launch_decay_rule_t<4, 16>(a, n_req, stream);
-    if (a.dim <= 128) return launch_decay_rule_t<4, 32>(a, n_req, stream);
-    if (a.dim <= 256) return launch_decay_rule_t<8, 32>(a, n_req, stream);
-    if (a.dim <= 512) return launch_decay_rule_t<16, 32>(a, n_req, stream);
-    return launch_decay_rule_t<32, 32>(a, n_req, stream);
+    int lpc = 4, dpt = 4;
+    while (dpt < 32 && lpc * dpt < a.dim) dpt *= 2;
+    while (lpc * dpt < a.dim) lpc *= 2;
+    auto ctas = [&](int l) { return (long long)n_req * a.heads * ((a.vd + RTHREADS / l - 1) / (RTHREADS / l)); };
+    while (lpc < 32 && dpt > 4 && ctas(lpc) < 2 * 148) { lpc *= 2; dpt /= 2; }
+#define FT_RULE(L, D) if (lpc == L && dpt == D) return launch_decay_rule_t<L, D>(a, n_req, stream)
+    FT_RULE(4, 4); FT_RULE(4, 8); FT_RULE(4, 16); FT_RULE(4, 32);
+    FT_RULE(8, 4); FT_RULE(8, 8); FT_RULE(8, 16); FT_RULE(8, 32);
+    FT_RULE(16, 4); FT_RULE(16, 8); FT_RULE(16, 16); FT_RULE(16, 32);
+    FT_RULE(32, 4); FT_RULE(32, 8); FT_RULE(32, 16); FT_RULE(32, 32);
+#undef FT_RULE
+    FT_REQUIRE(false, "decay rule: no kernel for %d lanes x %d channels", lpc, dpt);
+    return -1;
 }
 
 // ------------------------------------------------------------------ gated matrix memory: gates and the running maximum
@@ -366,31 +401,47 @@ __global__ void __launch_bounds__(128) memory_prep_kernel(MemoryArgs a) {
         a.gates[((size_t)t * a.heads + h) * 2 + 1] = gf;
     }
 }
-// One thread per (request, head) walks the request's tokens: m <- max(f + m, i); a = exp(f + m_old - m), b = exp(i - m);
-// floor[t] = exp(-m), the lower bound of the read-out's denominator.  m lives in the state slot, 0 at a sequence's start.
-__global__ void memory_scan_kernel(MemoryArgs a) {
-    const int r = blockIdx.x, h = threadIdx.x;
-    if (h >= a.heads) return;
+// One warp per (request, head): m_t = max(f_t + m_(t-1), i_t) is a scan under the associative rule
+// (F1, G1) o (F2, G2) = (F1 + F2, max(G1 + F2, G2)), so 32 tokens are taken at a time with shuffles and m enters each block as
+// m_t = max(F_t + m_in, G_t).  Then a = exp(f + m_(t-1) - m_t), b = exp(i - m_t), floor[t] = exp(-m_t), the lower bound of the
+// read-out's denominator.  m lives in the state slot, 0 at a sequence's start.
+__global__ void __launch_bounds__(128) memory_scan_kernel(MemoryArgs a, int n_units) {
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (unit >= n_units) return;
+    const int r = unit / a.heads, h = unit % a.heads;
     const int t0 = a.req_start[r], t1 = a.req_start[r + 1];
     if (t1 <= t0) return;
     float* ms = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.m_off + h;
     float m = a.req_pos0[r] > 0 ? *ms : 0.f;
-    for (int t = t0; t < t1; ++t) {
-        const size_t at = (size_t)t * a.heads + h;
-        const float gi = a.gates[2 * at], gf = a.gates[2 * at + 1];
-        const float mn = fmaxf(gf + m, gi);
-        a.ab[2 * at] = expf(gf + m - mn);
-        a.ab[2 * at + 1] = expf(gi - mn);
-        a.floor[at] = expf(-mn);
-        m = mn;
+    for (int b0 = t0; b0 < t1; b0 += 32) {
+        const int t = b0 + lane;
+        const bool in = t < t1;
+        const size_t at = (size_t)(in ? t : t1 - 1) * a.heads + h;
+        const float gi = in ? a.gates[2 * at] : -INFINITY, gf = in ? a.gates[2 * at + 1] : 0.f;
+        float F = gf, G = gi;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const float pF = __shfl_up_sync(0xffffffffu, F, off), pG = __shfl_up_sync(0xffffffffu, G, off);
+            if (lane >= off) { G = fmaxf(pG + F, G); F = pF + F; }
+        }
+        const float mt = fmaxf(F + m, G);
+        float mp = __shfl_up_sync(0xffffffffu, mt, 1);
+        if (lane == 0) mp = m;
+        if (in) {
+            a.ab[2 * at] = expf(gf + mp - mt);
+            a.ab[2 * at + 1] = expf(gi - mt);
+            a.floor[at] = expf(-mt);
+        }
+        m = __shfl_sync(0xffffffffu, mt, min(31, t1 - 1 - b0));
     }
-    *ms = m;
+    if (lane == 0) *ms = m;
 }
 int launch_memory_prep(const MemoryArgs& a, int T, int n_req, cudaStream_t stream) {
-    FT_REQUIRE(a.heads >= 1 && a.heads <= 1024 && a.cap > 0.f, "matrix memory: bad head count or gate cap");
+    FT_REQUIRE(a.heads >= 1 && a.cap > 0.f, "matrix memory: bad head count or gate cap");
     memory_prep_kernel<<<T, 128, 0, stream>>>(a);
     FT_CHECK_CUDA(cudaGetLastError());
-    memory_scan_kernel<<<n_req, ((a.heads + 31) / 32) * 32, 0, stream>>>(a);
+    const int units = n_req * a.heads;
+    memory_scan_kernel<<<(units + 3) / 4, 128, 0, stream>>>(a, units);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -423,11 +474,11 @@ __global__ void __launch_bounds__(256) space_conv_kernel(SpaceArgs a) {
 // The slot's tail after the step: the raw inputs of the last K-1 positions, from this step's rows or the old tail.
 constexpr int kMaxTaps = 16;
 __global__ void __launch_bounds__(256) space_tail_kernel(SpaceArgs a) {
-    const int r = blockIdx.x;
+    const int r = blockIdx.y;
     const int start = a.req_start[r], n = a.req_start[r + 1] - start, pos0 = a.req_pos0[r], K = a.taps;
     if (n <= 0 || K <= 1) return;
     float* tail = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.tail_off;
-    for (int c = threadIdx.x; c < a.channels; c += blockDim.x) {
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < a.channels; c += gridDim.x * blockDim.x) {
         float nv[kMaxTaps];
         for (int i = 0; i < K - 1; ++i) {
             const int k = n - (K - 1) + i;
@@ -443,13 +494,13 @@ int launch_space_prep(const SpaceArgs& a, int T, int n_req, cudaStream_t stream)
     FT_REQUIRE(a.taps >= 1 && a.taps <= kMaxTaps, "state space: 1 to %d convolution taps (got %d)", kMaxTaps, a.taps);
     space_conv_kernel<<<T, 256, 0, stream>>>(a);
     FT_CHECK_CUDA(cudaGetLastError());
-    space_tail_kernel<<<n_req, 256, 0, stream>>>(a);
+    space_tail_kernel<<<dim3((a.channels + 255) / 256, n_req), 256, 0, stream>>>(a);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
 
 // ------------------------------------------------------------------ read-out of the recurrent branches
-// One warp per (token, norm group).  Value of column c = (head h, j):
+// One CTA per (token, norm group).  Value of column c = (head h, j):
 //   o[t][h * vd + j] * q_scale                              (vd = vdim, or vdim + 1 with the normaliser in the last column)
 //   / (max(|o[t][h * vd + vdim] * q_scale|, floor[t][h]) + 1e-6)      with a normaliser
 //   + skip[h] * x[t][c]                                      with a skip
@@ -464,17 +515,24 @@ __device__ __forceinline__ float readout_value(const ReadoutArgs& a, int t, int 
     if (a.gate_kind == 1) v *= silu_f(a.gate[(size_t)t * a.ldg + c]);
     return v;
 }
-__global__ void __launch_bounds__(128) readout_kernel(ReadoutArgs a, int n_units) {
-    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (unit >= n_units) return;
-    const int t = unit / a.norm_groups, g = unit % a.norm_groups;
+constexpr int kReadoutKeep = 8;      // values a thread keeps in registers between the two passes
+__global__ void __launch_bounds__(256) readout_kernel(ReadoutArgs a) {
+    __shared__ float red[33];
+    const int t = blockIdx.x / a.norm_groups, g = blockIdx.x % a.norm_groups;
     const int n = a.heads * a.vdim / a.norm_groups, c0 = g * n;
+    float keep[kReadoutKeep];
     float ss = 0.f;
-    for (int c = lane; c < n; c += 32) { const float v = readout_value(a, t, c0 + c); ss = fmaf(v, v, ss); }
-    ss = warp_sum(ss);
+    int i = 0;
+    for (int c = threadIdx.x; c < n; c += blockDim.x, ++i) {
+        const float v = readout_value(a, t, c0 + c);
+        if (i < kReadoutKeep) keep[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = blockDim.x == 32 ? warp_sum(ss) : cta_sum(ss, red);
     const float rr = 1.f / sqrtf(ss / (float)n + a.eps);
-    for (int c = lane; c < n; c += 32) {
-        float v = readout_value(a, t, c0 + c) * rr * a.gain[c0 + c];
+    i = 0;
+    for (int c = threadIdx.x; c < n; c += blockDim.x, ++i) {
+        float v = (i < kReadoutKeep ? keep[i] : readout_value(a, t, c0 + c)) * rr * a.gain[c0 + c];
         if (a.gate_kind == 2) v *= sigmoid_f(a.gate[(size_t)t * a.ldg + c0 + c]);
         a.out[(size_t)t * a.heads * a.vdim + c0 + c] = v;
     }
@@ -482,8 +540,9 @@ __global__ void __launch_bounds__(128) readout_kernel(ReadoutArgs a, int n_units
 int launch_readout(const ReadoutArgs& a, int T, cudaStream_t stream) {
     FT_REQUIRE(a.norm_groups >= 1 && (a.heads * a.vdim) % a.norm_groups == 0, "read-out: %d columns do not split into %d norm groups",
                a.heads * a.vdim, a.norm_groups);
-    const int units = T * a.norm_groups;
-    readout_kernel<<<(units + 3) / 4, 128, 0, stream>>>(a, units);
+    const int n = a.heads * a.vdim / a.norm_groups;
+    const int threads = n <= 64 ? 32 : n <= 256 ? 64 : n <= 1024 ? 128 : 256;
+    readout_kernel<<<T * a.norm_groups, threads, 0, stream>>>(a);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

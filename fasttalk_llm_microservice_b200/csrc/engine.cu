@@ -857,12 +857,11 @@ static int forward_layered(Engine* e, const Batch& b) {
                     FT_TRY(run_mlp(e, hn_hi, hn_lo, c.w_gu, c.w_down, c.ff, c.ff_act, L.mix, T));
                     sf.y0 = L.mix;
                 } else {
-                    LinearArgs r;                   // router logits in fp32, whatever the form of the other products
-                    r.A = L.hn; r.lda = W; r.W = (const __nv_bfloat16*)c.w_router; r.ldw = W; r.C = L.rlog; r.ldc = c.experts;
-                    r.M = T; r.N = c.experts; r.K = W;
-                    FT_TRY(launch_linear(r, T, st));
-                    launched();
-                    FT_TRY(run_experts(e, c, L.rlog, c.experts, 0, T));
+                    // router logits: fp32 accumulation over fp32 activations (CUDA cores), or over their bf16 hi + lo planes
+                    // on the tensor cores when the step is large; the router's rows are padded to whole tiles for that
+                    const int ldl = c.router_rows > 0 ? c.router_rows : c.experts;
+                    FT_TRY(dense(e, L.hn, hn_hi, hn_lo, c.w_router, L.rlog, T, ldl, W));
+                    FT_TRY(run_experts(e, c, L.rlog, ldl, 0, T));
                     sf.eout = L.eout; sf.wt = L.wts; sf.slot_pos = L.slot_pos; sf.top = c.top;
                     if (c.shared_ff > 0) {
                         FT_TRY(run_mlp(e, hn_hi, hn_lo, c.w_shared_up, c.w_shared_down, c.shared_ff, c.ff_act, L.mix, T));
@@ -1503,7 +1502,8 @@ static int engine_init_layered(Engine* e) {
                        "engine: layer %d lacks the shared expert's weights", l);
             top_max = std::max(top_max, d.top);
             act_cols = std::max(act_cols, (size_t)std::max(d.ff, sandwich ? d.shared_ff : 0));
-            e_max_s = std::max(e_max_s, (size_t)d.experts);
+            FT_REQUIRE(d.router_rows == 0 || d.router_rows >= d.experts, "engine: layer %d: router_rows below the expert count", l);
+            e_max_s = std::max(e_max_s, (size_t)std::max(d.experts, d.router_rows));
         } else if (d.ff_kind == FT_FF_DENSE) {
             FT_REQUIRE(sandwich && d.ff >= 1 && d.w_gu && d.w_down, "engine: dense feed-forward layer %d is incomplete", l);
             act_cols = std::max(act_cols, (size_t)d.ff);

@@ -410,7 +410,7 @@ class LayerDesc(C.Structure):
         ("form", C.c_int), ("n_branches", C.c_int), ("branch", BranchDesc * 2),
         ("norm_pre1", C.c_void_p), ("norm_post1", C.c_void_p), ("norm_pre2", C.c_void_p), ("norm_post2", C.c_void_p),
         ("ff_act", C.c_int), ("route_kind", C.c_int), ("route_norm", C.c_int), ("route_scale", C.c_float),
-        ("w_router", C.c_void_p), ("shared_ff", C.c_int), ("w_shared_up", C.c_void_p), ("w_shared_down", C.c_void_p),
+        ("w_router", C.c_void_p), ("router_rows", C.c_int), ("shared_ff", C.c_int), ("w_shared_up", C.c_void_p), ("w_shared_down", C.c_void_p),
     ]
 
 
@@ -525,7 +525,9 @@ def _pack_sandwich_layer(l: LayerSpec, w: Dict[str, torch.Tensor], p: str, d, W:
     elif l.ff_kind == "moe":
         d.ff_kind, d.ff_act, d.experts, d.top, d.groups, d.keep = FF_MOE, ACT_RELU2, l.experts, l.top, 1, 1
         d.route_kind, d.route_norm, d.route_scale = ROUTE_SIGMOID, 1, l.route_scale
-        d.w_router = dev(w[p + "mlp.router"]).data_ptr()
+        router = torch.zeros((l.experts + 127) // 128 * 128, W, dtype=torch.bfloat16, device=device)
+        router[:l.experts] = w[p + "mlp.router"].to(device)
+        d.w_router, d.router_rows = dev(router).data_ptr(), router.shape[0]
         d.w_gu = dev(torch.stack([w[f"{p}mlp.e{e}.up"].to(device) for e in range(l.experts)])).data_ptr()
         d.w_down = dev(torch.stack([w[f"{p}mlp.e{e}.down"].to(device) for e in range(l.experts)])).data_ptr()
         if l.shared_ff:

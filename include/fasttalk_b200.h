@@ -286,7 +286,8 @@ typedef struct {
     int route_kind;            /* FT_ROUTE_* */
     int route_norm;            /* 1: the chosen scores are divided by their sum (+ 1e-20) */
     float route_scale;         /* then multiplied by this (0 = 1) */
-    const void* w_router;      /* bf16 [experts][width] */
+    const void* w_router;      /* bf16 [max(experts, router_rows)][width] */
+    int router_rows;           /* 0, or the rows of w_router when it is padded with zero rows to whole GEMM tiles */
     int shared_ff;             /* 0 = no shared expert */
     const void* w_shared_up;   /* bf16 [shared_ff (x 2, paired, for FT_ACT_SWIGLU)][width] */
     const void* w_shared_down; /* bf16 [width][shared_ff] */
