@@ -220,7 +220,172 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs 
     }
 }
 
-int launch_window_attention(const WindowArgs& a, int T, cudaStream_t stream) {
+// Prompt portions: one CTA per (key head, run of QT consecutive tokens of one request), QT = 64 / (query heads per key head),
+// so that up to 64 query rows — the tokens of the run times the query heads of the group — share every key and value row
+// that is brought into shared memory.  Keys are taken 32 at a time from the first one the run's first token sees to the
+// run's last position: S = Q K^T (each thread 2 rows x 4 keys, keys interleaved by 8 so that the 16-byte reads of a warp fall
+// into different banks), cap, per-row window mask, online softmax (a row's 8 threads are neighbouring lanes), P to shared
+// memory, O = O * corr + P V (each warp 8 rows, each lane 4 value columns per 128).  All of it in fp32.
+constexpr int WT_ROWS = 64, WT_KEYS = 32, WT_THREADS = 256;
+template <int VK>
+__global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, WindowTiles tm, int QT, int subs) {
+    extern __shared__ __align__(16) float wsh[];
+    const int ldq = a.dim + 4, ldv = a.vdim, ldp = WT_KEYS + 1;
+    float* Qs = wsh;                          // [64][dim + 4]
+    float* Ks = Qs + WT_ROWS * ldq;           // [32][dim + 4]
+    float* Vs = Ks + WT_KEYS * ldq;           // [32][vdim]
+    float* Ps = Vs + WT_KEYS * ldv;           // [64][33]
+    float* cr = Ps + WT_ROWS * ldp;           // [64] rescale of a row's sums in this tile; at the end the row's softmax sum
+    const int tile = blockIdx.x / subs, sub = blockIdx.x % subs, g = blockIdx.y, tid = threadIdx.x;
+    const int j = tm.tile_req[tile];
+    const int q0 = tm.tile_q0[tile] + sub * QT;
+    const int n_j = tm.req_q_start[j + 1] - tm.req_q_start[j];
+    if (sub * QT >= 64 || q0 >= n_j) return;
+    const int ntok = min(QT, min(n_j - q0, 64 - sub * QT));
+    const int row_base = tm.req_q_start[j] + q0, p_first = tm.req_pos0[j] + q0;
+    const int* pt = a.page_table + (size_t)tm.req_slot[j] * a.max_pages;
+    const int grp = a.H / a.G, rows_used = ntok * grp;
+    const size_t rowsz = (size_t)a.G * (a.dim + a.vdim);
+    const int d4n = a.dim >> 2, v4n = a.vdim >> 2;
+    for (int i = tid; i < WT_ROWS * d4n; i += WT_THREADS) {
+        const int r = i / d4n, d4 = i - r * d4n;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < rows_used)
+            v = *reinterpret_cast<const float4*>(a.q_out + ((size_t)(row_base + r / grp) * a.H + g * grp + r % grp) * a.dim + 4 * d4);
+        *reinterpret_cast<float4*>(Qs + r * ldq + 4 * d4) = v;
+    }
+    const int lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0, hi = p_first + ntok - 1;
+    const int ry = tid >> 3, cx = tid & 7;            // scores: rows 2 ry, 2 ry + 1; keys cx, cx + 8, cx + 16, cx + 24 of the tile
+    const int oy = tid >> 5, ox = tid & 31;           // sums: rows 8 oy .. 8 oy + 7; columns 4 ox .. 4 ox + 3 (+ 128)
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    int pr[2];
+    bool rv[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) { rv[i] = 2 * ry + i < rows_used; pr[i] = p_first + (2 * ry + i) / grp; }
+    float acc[8][VK][4];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+        for (int k = 0; k < VK; ++k)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[r][k][c] = 0.f;
+    for (int k0 = lo; k0 <= hi; k0 += WT_KEYS) {
+        __syncthreads();                               // the last tile's sums are done with Ks / Vs / Ps
+        for (int i = tid; i < WT_KEYS * d4n; i += WT_THREADS) {
+            const int c = i / d4n, d4 = i - c * d4n, key = k0 + c;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (key <= hi)
+                v = *reinterpret_cast<const float4*>(a.cache + ((size_t)pt[key >> 6] * 64 + (key & 63)) * rowsz + (size_t)g * a.dim + 4 * d4);
+            *reinterpret_cast<float4*>(Ks + c * ldq + 4 * d4) = v;
+        }
+        for (int i = tid; i < WT_KEYS * v4n; i += WT_THREADS) {
+            const int c = i / v4n, d4 = i - c * v4n, key = k0 + c;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (key <= hi)
+                v = *reinterpret_cast<const float4*>(a.cache + ((size_t)pt[key >> 6] * 64 + (key & 63)) * rowsz + (size_t)a.G * a.dim +
+                                                     (size_t)g * a.vdim + 4 * d4);
+            *reinterpret_cast<float4*>(Vs + c * ldv + 4 * d4) = v;
+        }
+        __syncthreads();
+        float sc[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) sc[i][c] = 0.f;
+        for (int d4 = 0; d4 < d4n; ++d4) {
+            const float4 q0v = *reinterpret_cast<const float4*>(Qs + (2 * ry) * ldq + 4 * d4);
+            const float4 q1v = *reinterpret_cast<const float4*>(Qs + (2 * ry + 1) * ldq + 4 * d4);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float4 kv = *reinterpret_cast<const float4*>(Ks + (cx + 8 * c) * ldq + 4 * d4);
+                sc[0][c] = fmaf(q0v.x, kv.x, sc[0][c]); sc[0][c] = fmaf(q0v.y, kv.y, sc[0][c]);
+                sc[0][c] = fmaf(q0v.z, kv.z, sc[0][c]); sc[0][c] = fmaf(q0v.w, kv.w, sc[0][c]);
+                sc[1][c] = fmaf(q1v.x, kv.x, sc[1][c]); sc[1][c] = fmaf(q1v.y, kv.y, sc[1][c]);
+                sc[1][c] = fmaf(q1v.z, kv.z, sc[1][c]); sc[1][c] = fmaf(q1v.w, kv.w, sc[1][c]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int key = k0 + cx + 8 * c;
+                float v = sc[i][c] * a.scale;
+                if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+                const bool vis = rv[i] && key <= pr[i] && (a.window <= 0 || key > pr[i] - a.window);
+                sc[i][c] = vis ? v : -INFINITY;
+                tmax = fmaxf(tmax, sc[i][c]);
+            }
+#pragma unroll
+            for (int off = 1; off < 8; off <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, off));
+            const float m_new = fmaxf(m[i], tmax);
+            float corr = 1.f, psum = 0.f;
+            if (m_new == -INFINITY) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) sc[i][c] = 0.f;
+            } else {
+                corr = expf(m[i] - m_new);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) { sc[i][c] = expf(sc[i][c] - m_new); psum += sc[i][c]; }
+            }
+#pragma unroll
+            for (int off = 1; off < 8; off <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, off);
+            l[i] = l[i] * corr + psum;
+            m[i] = m_new;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) Ps[(2 * ry + i) * ldp + cx + 8 * c] = sc[i][c];
+            if (cx == 0) cr[2 * ry + i] = corr;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const float f = cr[8 * oy + r];
+#pragma unroll
+            for (int k = 0; k < VK; ++k)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[r][k][c] *= f;
+        }
+        for (int c = 0; c < WT_KEYS; ++c) {
+            float4 vv[VK];
+#pragma unroll
+            for (int k = 0; k < VK; ++k) {
+                const int col = 4 * ox + 128 * k;
+                vv[k] = col < a.vdim ? *reinterpret_cast<const float4*>(Vs + c * ldv + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const float pv = Ps[(8 * oy + r) * ldp + c];
+#pragma unroll
+                for (int k = 0; k < VK; ++k) {
+                    acc[r][k][0] = fmaf(pv, vv[k].x, acc[r][k][0]); acc[r][k][1] = fmaf(pv, vv[k].y, acc[r][k][1]);
+                    acc[r][k][2] = fmaf(pv, vv[k].z, acc[r][k][2]); acc[r][k][3] = fmaf(pv, vv[k].w, acc[r][k][3]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (cx == 0) { cr[2 * ry] = l[0]; cr[2 * ry + 1] = l[1]; }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        const int row = 8 * oy + r;
+        if (row >= rows_used) continue;
+        const float inv = 1.f / cr[row];
+        float* orow = a.out + ((size_t)(row_base + row / grp) * a.H + g * grp + row % grp) * a.vdim;
+#pragma unroll
+        for (int k = 0; k < VK; ++k) {
+            const int col = 4 * ox + 128 * k;
+            if (col < a.vdim)
+                *reinterpret_cast<float4*>(orow + col) =
+                    make_float4(acc[r][k][0] * inv, acc[r][k][1] * inv, acc[r][k][2] * inv, acc[r][k][3] * inv);
+        }
+    }
+}
+
+// n_single: the step's first rows that are single tokens of running sequences (one CTA per (token, head) each); the prompt
+// portions that follow them run on the tiled kernel when the head sizes allow it (multiples of 4, at most 64 query heads
+// per key head), otherwise like the single tokens.
+int launch_window_attention(const WindowArgs& a, int T, int n_single, const WindowTiles& tm, cudaStream_t stream) {
     FT_REQUIRE(a.H >= 1 && a.G >= 1 && a.H % a.G == 0 && a.dim >= 1 && a.vdim >= 1 && a.vdim <= 256,
                "window attention: bad head sizes (heads %d, kv heads %d, dim %d, vdim %d)", a.H, a.G, a.dim, a.vdim);
     FT_REQUIRE(a.rot_dims >= 0 && a.rot_dims <= a.dim && (a.rot_dims & 1) == 0 && (a.rot_dims == 0 || (a.dim & 1) == 0),
@@ -228,6 +393,25 @@ int launch_window_attention(const WindowArgs& a, int T, cudaStream_t stream) {
     FT_REQUIRE(a.o_v >= 0 || a.vdim == a.dim, "window attention: keys used as values need vdim == dim");
     window_write_kernel<<<T, 128, 0, stream>>>(a);
     FT_CHECK_CUDA(cudaGetLastError());
+    const int grp = a.H / a.G;
+    const size_t tsm = (size_t)((WT_ROWS + WT_KEYS) * (a.dim + 4) + WT_KEYS * a.vdim + WT_ROWS * (WT_KEYS + 1) + WT_ROWS) * 4;
+    const bool tiled = tm.n_tiles > 0 && (a.dim & 3) == 0 && (a.vdim & 3) == 0 && grp <= WT_ROWS && tsm <= 200 * 1024;
+    int rows_each = T;                                 // rows of the one-CTA-per-(token, head) kernel
+    if (tiled) {
+        rows_each = n_single;
+        const int QT = WT_ROWS / grp, subs = (64 + QT - 1) / QT;
+        dim3 grid(tm.n_tiles * subs, a.G);
+        if (a.vdim <= 128) {
+            FT_CHECK_CUDA(cudaFuncSetAttribute(window_tile_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsm));
+            window_tile_kernel<1><<<grid, WT_THREADS, tsm, stream>>>(a, tm, QT, subs);
+        } else {
+            FT_CHECK_CUDA(cudaFuncSetAttribute(window_tile_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsm));
+            window_tile_kernel<2><<<grid, WT_THREADS, tsm, stream>>>(a, tm, QT, subs);
+        }
+        FT_CHECK_CUDA(cudaGetLastError());
+    }
+    if (rows_each <= 0) return 0;
+    T = rows_each;
     const size_t smem = (size_t)(((a.dim + 3) & ~3) + 2 * kWinWarps + kWinWarps * a.vdim) * 4;
     const bool vec = (a.dim & 3) == 0 && (a.vdim & 3) == 0;      // every key row then starts on 16 bytes
     dim3 grid(a.H, T);
@@ -256,7 +440,11 @@ constexpr int RCH = 8, RTHREADS = 128;
 __device__ __forceinline__ void cp_async_f32(float* dst_smem, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
 }
-template <int LPC, int DPT>
+__device__ __forceinline__ void cp_async_f32x4(float* dst_smem, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+// VEC: keys and queries are copied 16 bytes at a time (dim a multiple of 4, rows and bases on 16-byte boundaries)
+template <int LPC, int DPT, bool VEC>
 __global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
     constexpr int VB = RTHREADS / LPC, RUN = DPT + 4, DP = LPC * RUN;
     constexpr int BUF = 2 * RCH * DP + RCH * VB + RCH * 2;      // floats of one staged chunk: keys | queries | values | (a, b)
@@ -282,11 +470,23 @@ __global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
         float* sv = sq + RCH * DP;
         float* sab = sv + RCH * VB;
         const int nt = min(RCH, t1 - c0);
-        for (int i = threadIdx.x; i < nt * a.dim; i += RTHREADS) {
-            const int tt = i / a.dim, d = i - tt * a.dim;
-            const int at = tt * DP + (d / DPT) * RUN + (d % DPT);
-            cp_async_f32(sk + at, a.k + (size_t)(c0 + tt) * a.ldk + (size_t)gh * a.dim + d);
-            cp_async_f32(sq + at, a.q + (size_t)(c0 + tt) * a.ldq + (size_t)gh * a.dim + d);
+        if (VEC) {                                   // a warp per token row, a lane per four channels
+            for (int tt = threadIdx.x >> 5; tt < nt; tt += RTHREADS / 32) {
+                const float* kr = a.k + (size_t)(c0 + tt) * a.ldk + (size_t)gh * a.dim;
+                const float* qr = a.q + (size_t)(c0 + tt) * a.ldq + (size_t)gh * a.dim;
+                for (int d = (threadIdx.x & 31) * 4; d < a.dim; d += 128) {
+                    const int at = tt * DP + (d / DPT) * RUN + (d % DPT);
+                    cp_async_f32x4(sk + at, kr + d);
+                    cp_async_f32x4(sq + at, qr + d);
+                }
+            }
+        } else {
+            for (int i = threadIdx.x; i < nt * a.dim; i += RTHREADS) {
+                const int tt = i / a.dim, d = i - tt * a.dim;
+                const int at = tt * DP + (d / DPT) * RUN + (d % DPT);
+                cp_async_f32(sk + at, a.k + (size_t)(c0 + tt) * a.ldk + (size_t)gh * a.dim + d);
+                cp_async_f32(sq + at, a.q + (size_t)(c0 + tt) * a.ldq + (size_t)gh * a.dim + d);
+            }
         }
         for (int i = threadIdx.x; i < nt * VB; i += RTHREADS) {
             const int tt = i / VB, c = i % VB;
@@ -352,10 +552,14 @@ template <int LPC, int DPT>
 static int launch_decay_rule_t(const RecurArgs& a, int n_req, cudaStream_t stream) {
     constexpr int VB = RTHREADS / LPC, DP = LPC * (DPT + 4);
     const size_t smem = (size_t)2 * (2 * RCH * DP + RCH * VB + RCH * 2) * 4;
-    if (smem > 48 * 1024)
-        FT_CHECK_CUDA(cudaFuncSetAttribute(decay_rule_kernel<LPC, DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const bool vec = (a.dim & 3) == 0 && (a.ldk & 3) == 0 && (a.ldq & 3) == 0 && ((uintptr_t)a.k & 15) == 0 && ((uintptr_t)a.q & 15) == 0;
+    if (smem > 48 * 1024) {
+        FT_CHECK_CUDA(cudaFuncSetAttribute(decay_rule_kernel<LPC, DPT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FT_CHECK_CUDA(cudaFuncSetAttribute(decay_rule_kernel<LPC, DPT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
     dim3 grid((a.vd + VB - 1) / VB, a.heads, n_req);
-    decay_rule_kernel<LPC, DPT><<<grid, RTHREADS, smem, stream>>>(a);
+    if (vec) decay_rule_kernel<LPC, DPT, true><<<grid, RTHREADS, smem, stream>>>(a);
+    else decay_rule_kernel<LPC, DPT, false><<<grid, RTHREADS, smem, stream>>>(a);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

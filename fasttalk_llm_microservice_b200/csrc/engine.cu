@@ -708,8 +708,11 @@ static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, 
         a.positions = d + m.o_pos; a.seq_rows = d + m.o_rows; a.page_table = d + m.o_pt; a.max_pages = e->max_pages;
         a.H = c.heads; a.G = c.kv_heads; a.dim = c.dim; a.vdim = c.vdim; a.window = c.window;
         a.scale = c.scale; a.softcap = c.softcap; a.out = L.bfin;
-        FT_TRY(launch_window_attention(a, T, st));
-        launched(2);
+        WindowTiles tm;
+        tm.tile_req = d + m.o_treq; tm.tile_q0 = d + m.o_tq0; tm.req_q_start = d + m.o_qstart; tm.req_slot = d + m.o_rslot;
+        tm.req_pos0 = d + m.o_rpos0; tm.n_tiles = b.n_tiles;
+        FT_TRY(launch_window_attention(a, T, b.n_decode, tm, st));
+        launched(b.n_tiles > 0 && b.n_decode > 0 ? 3 : 2);
     } else {
         RecurArgs r;
         r.ab = L.ab; r.o = L.bo; r.state = L.state; r.slot_stride = (long long)L.slot_stride; r.s_off = (long long)ll.br_s_off[k];

@@ -200,7 +200,14 @@ struct WindowArgs {
     float scale = 1.f, softcap = 0.f;
     float* out = nullptr;                         // [T][H * vdim]
 };
-int launch_window_attention(const WindowArgs& a, int T, cudaStream_t stream);
+// The step's prompt portions as the batch builder lists them: 64-token query tiles (request, first token), and per request
+// its first row in the step, its page-table row and the position of its first token.
+struct WindowTiles {
+    const int *tile_req = nullptr, *tile_q0 = nullptr, *req_q_start = nullptr, *req_slot = nullptr, *req_pos0 = nullptr;
+    int n_tiles = 0;
+};
+// n_single: how many of the step's first rows are single tokens of running sequences (they precede the portions)
+int launch_window_attention(const WindowArgs& a, int T, int n_single, const WindowTiles& tm, cudaStream_t stream);
 
 // S <- a_t S + b_t k_t v_t^T, o_t = S^T q_t per (request, head) over the request's rows in order; S [dim][vd] of head h at
 // state + slot * slot_stride + s_off + h * dim * vd, zero at a sequence's start (req_pos0 == 0).
