@@ -432,11 +432,34 @@ int launch_window_attention(const WindowArgs& a, int T, int n_single, const Wind
 
 // ------------------------------------------------------------------ scalar-decay rule
 // Lanes s = 0..LPC-1 of a column hold channels s * DPT .. s * DPT + DPT - 1 of that column of S.  Chunks of RCH tokens are
-// staged in shared memory one chunk ahead with asynchronous copies (keys and queries padded with zeros to LPC * DPT
-// channels, each lane's run 4 floats apart from the next so that the 16-byte reads of the LPC runs fall into different
-// banks), then the tokens of a chunk are taken in order.  The state is the only dependence from token to token; the
+// staged in two shared-memory buffers one chunk ahead with asynchronous copies (keys and queries padded with zeros
+// to LPC * DPT channels, each lane's run 4 floats apart from the next so that the 16-byte reads of the LPC runs fall into
+// different banks), then the tokens of a chunk are taken in order.  A full chunk runs without a branch, so that the
+// compiler can start the shared-memory reads of later tokens under the arithmetic of earlier ones, and the arithmetic
+// itself is packed: two neighbouring channels of a column share every multiply-add (fma.rn.f32x2, the two-wide fp32
+// form of sm_100; each half rounds as the scalar instruction does).  The state is the only dependence from token to token; the
 // read-out o_t = S^T q_t (partial sums over a lane's run, then a shuffle tree over the LPC lanes) overlaps the next update.
-constexpr int RCH = 8, RTHREADS = 128;
+constexpr int RCH = 16, RTHREADS = 128;
+// stages of the ring for a padded row of DP floats: as deep as ~100-160 KB of shared memory allow
+__host__ __device__ constexpr int rule_stages(int dp) { return 2; }
+typedef unsigned long long f32x2;      // two fp32 numbers in one 64-bit register
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+template <int N> __device__ __forceinline__ void cp_async_wait_pending() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void cp_async_f32(float* dst_smem, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
 }
@@ -448,6 +471,7 @@ template <int LPC, int DPT, bool VEC>
 __global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
     constexpr int VB = RTHREADS / LPC, RUN = DPT + 4, DP = LPC * RUN;
     constexpr int BUF = 2 * RCH * DP + RCH * VB + RCH * 2;      // floats of one staged chunk: keys | queries | values | (a, b)
+    constexpr int NST = rule_stages(DP);
     extern __shared__ __align__(16) float rs[];
     const int r = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * VB;
     const int s = threadIdx.x % LPC, jl = threadIdx.x / LPC, j = j0 + jl;
@@ -456,15 +480,18 @@ __global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
     const int gh = h / (a.heads / a.qk_heads);
     float* S = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.s_off + (size_t)h * a.dim * a.vd;
     const bool live = j < a.vd;
-    for (int i = threadIdx.x; i < 2 * BUF; i += RTHREADS) rs[i] = 0.f;      // the padding stays zero from here on
-    float st[DPT];
+    if (LPC * DPT != a.dim || j0 + VB > a.vd)                                  // the padding stays zero from here on
+        for (int i = threadIdx.x; i < NST * BUF; i += RTHREADS) rs[i] = 0.f;
+    f32x2 st[DPT / 2];                       // channels (2 i, 2 i + 1) of the lane's run
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) {
+    for (int i = 0; i < DPT; i += 2) {
         const int d = s * DPT + i;
-        st[i] = (a.req_pos0[r] > 0 && live && d < a.dim) ? S[(size_t)d * a.vd + j] : 0.f;
+        const bool old = a.req_pos0[r] > 0 && live;
+        st[i / 2] = pack2(old && d < a.dim ? S[(size_t)d * a.vd + j] : 0.f, old && d + 1 < a.dim ? S[(size_t)(d + 1) * a.vd + j] : 0.f);
     }
     __syncthreads();
-    auto stage = [&](int buf, int c0) {
+    auto stage = [&](int buf, int c0) {          // always commits a group, an empty one past the end: the count stays uniform
+        if (c0 >= t1) { asm volatile("cp.async.commit_group;" ::: "memory"); return; }
         float* sk = rs + buf * BUF;
         float* sq = sk + RCH * DP;
         float* sv = sq + RCH * DP;
@@ -496,54 +523,56 @@ __global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
             cp_async_f32(sab + i, a.ab + ((size_t)(c0 + i / 2) * a.heads + h) * 2 + (i & 1));
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    stage(0, t0);
+#pragma unroll
+    for (int i = 0; i < NST - 1; ++i) stage(i, t0 + i * RCH);
     int buf = 0;
-    for (int c0 = t0; c0 < t1; c0 += RCH, buf ^= 1) {
+    for (int c0 = t0; c0 < t1; c0 += RCH, buf = buf + 1 == NST ? 0 : buf + 1) {
         const int nt = min(RCH, t1 - c0);
-        if (c0 + RCH < t1) {
-            stage(buf ^ 1, c0 + RCH);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
+        stage(buf == 0 ? NST - 1 : buf - 1, c0 + (NST - 1) * RCH);      // into the buffer the last iteration has finished with
+        cp_async_wait_pending<NST - 1>();
         __syncthreads();
         const float* sk = rs + buf * BUF;
         const float* sq = sk + RCH * DP;
         const float* sv = sq + RCH * DP;
         const float* sab = sv + RCH * VB;
+        auto token = [&](int tt) {
+            const float da = sab[2 * tt], bv = sab[2 * tt + 1] * sv[tt * VB + jl];
+            const f32x2 da2 = pack2(da, da), bv2 = pack2(bv, bv);
+            const ulonglong2* kp = reinterpret_cast<const ulonglong2*>(sk + tt * DP + s * RUN);
+            const ulonglong2* qp = reinterpret_cast<const ulonglong2*>(sq + tt * DP + s * RUN);
+            f32x2 o0 = 0ull, o1 = 0ull;
 #pragma unroll
-        for (int tt = 0; tt < RCH; ++tt) {
-            if (tt < nt) {
-                const float da = sab[2 * tt], bv = sab[2 * tt + 1] * sv[tt * VB + jl];
-                const float* kp = sk + tt * DP + s * RUN;
-                const float* qp = sq + tt * DP + s * RUN;
-                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-#pragma unroll
-                for (int i = 0; i < DPT; i += 4) {
-                    const float4 kv = *reinterpret_cast<const float4*>(kp + i);
-                    const float4 qv = *reinterpret_cast<const float4*>(qp + i);
-                    st[i] = fmaf(da, st[i], bv * kv.x);
-                    st[i + 1] = fmaf(da, st[i + 1], bv * kv.y);
-                    st[i + 2] = fmaf(da, st[i + 2], bv * kv.z);
-                    st[i + 3] = fmaf(da, st[i + 3], bv * kv.w);
-                    o0 = fmaf(st[i], qv.x, o0);
-                    o1 = fmaf(st[i + 1], qv.y, o1);
-                    o2 = fmaf(st[i + 2], qv.z, o2);
-                    o3 = fmaf(st[i + 3], qv.w, o3);
-                }
-                float o = (o0 + o1) + (o2 + o3);
-#pragma unroll
-                for (int off = LPC / 2; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-                if (s == 0 && live) a.o[(size_t)(c0 + tt) * a.ldo + (size_t)h * a.vd + j] = o;
+            for (int i = 0; i < DPT / 4; ++i) {
+                const ulonglong2 kv = kp[i], qv = qp[i];
+                st[2 * i] = fma2(da2, st[2 * i], mul2(bv2, kv.x));
+                st[2 * i + 1] = fma2(da2, st[2 * i + 1], mul2(bv2, kv.y));
+                o0 = fma2(st[2 * i], qv.x, o0);
+                o1 = fma2(st[2 * i + 1], qv.y, o1);
             }
+            float p0, p1, p2, p3;
+            unpack2(o0, p0, p1);
+            unpack2(o1, p2, p3);
+            float o = (p0 + p2) + (p1 + p3);
+#pragma unroll
+            for (int off = LPC / 2; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+            if (s == 0 && live) a.o[(size_t)(c0 + tt) * a.ldo + (size_t)h * a.vd + j] = o;
+        };
+        if (nt == RCH) {
+#pragma unroll 8
+            for (int tt = 0; tt < RCH; ++tt) token(tt);
+        } else {
+            for (int tt = 0; tt < nt; ++tt) token(tt);
         }
         __syncthreads();
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) {
+        for (int i = 0; i < DPT; i += 2) {
             const int d = s * DPT + i;
-            if (d < a.dim) S[(size_t)d * a.vd + j] = st[i];
+            float lo, hi;
+            unpack2(st[i / 2], lo, hi);
+            if (d < a.dim) S[(size_t)d * a.vd + j] = lo;
+            if (d + 1 < a.dim) S[(size_t)(d + 1) * a.vd + j] = hi;
         }
     }
 }
@@ -551,7 +580,7 @@ __global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
 template <int LPC, int DPT>
 static int launch_decay_rule_t(const RecurArgs& a, int n_req, cudaStream_t stream) {
     constexpr int VB = RTHREADS / LPC, DP = LPC * (DPT + 4);
-    const size_t smem = (size_t)2 * (2 * RCH * DP + RCH * VB + RCH * 2) * 4;
+    const size_t smem = (size_t)rule_stages(DP) * (2 * RCH * DP + RCH * VB + RCH * 2) * 4;
     const bool vec = (a.dim & 3) == 0 && (a.ldk & 3) == 0 && (a.ldq & 3) == 0 && ((uintptr_t)a.k & 15) == 0 && ((uintptr_t)a.q & 15) == 0;
     if (smem > 48 * 1024) {
         FT_CHECK_CUDA(cudaFuncSetAttribute(decay_rule_kernel<LPC, DPT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -565,9 +594,10 @@ static int launch_decay_rule_t(const RecurArgs& a, int n_req, cudaStream_t strea
 }
 
 // Lanes per column and channels per lane: the fewest lanes whose runs (<= 32 channels) cover dim — the widest column
-// blocks and the best-coalesced state traffic, what a step of many requests wants — and more lanes with shorter runs while
-// the grid would leave most of the GPU idle (one long prompt).  The split changes the order of a sum, nothing else.
-int launch_decay_rule(const RecurArgs& a, int n_req, cudaStream_t stream) {
+// blocks and the best-coalesced state traffic, what a step of single tokens wants — and more lanes with shorter runs for
+// prompt portions and while the grid would leave most of the GPU idle.  The split changes the order of a sum, nothing else.
+// T: tokens in the step (only a hint for that choice).
+int launch_decay_rule(const RecurArgs& a, int n_req, int T, cudaStream_t stream) {
     FT_REQUIRE(a.heads >= 1 && a.qk_heads >= 1 && a.heads % a.qk_heads == 0 && a.dim >= 1 && a.dim <= 1024 && a.vd >= 1,
                "decay rule: bad sizes (heads %d, key heads %d, dim %d, values %d)", a.heads, a.qk_heads, a.dim, a.vd);
     if (n_req <= 0) return 0;
@@ -575,7 +605,16 @@ int launch_decay_rule(const RecurArgs& a, int n_req, cudaStream_t stream) {
     while (dpt < 32 && lpc * dpt < a.dim) dpt *= 2;
     while (lpc * dpt < a.dim) lpc *= 2;
     auto ctas = [&](int l) { return (long long)n_req * a.heads * ((a.vd + RTHREADS / l - 1) / (RTHREADS / l)); };
-    while (lpc < 32 && dpt > 4 && ctas(lpc) < 2 * 148) { lpc *= 2; dpt /= 2; }
+    if (a.lanes > 0) {
+        FT_REQUIRE((a.lanes == 4 || a.lanes == 8 || a.lanes == 16 || a.lanes == 32) && a.lanes >= lpc,
+                   "decay rule: %d lanes per column do not hold %d channels", a.lanes, a.dim);
+        while (lpc < a.lanes && dpt > 4) { lpc *= 2; dpt /= 2; }
+    } else {
+        // prompt portions (many tokens per request): runs of at most 16 channels keep a token's arithmetic short; then
+        // more lanes while less than one CTA per SM would run
+        if (T >= 32 * n_req && lpc < 32 && dpt > 16) { lpc *= 2; dpt /= 2; }
+        while (lpc < 32 && dpt > 8 && ctas(lpc) < 96) { lpc *= 2; dpt /= 2; }
+    }
 #define FT_RULE(L, D) if (lpc == L && dpt == D) return launch_decay_rule_t<L, D>(a, n_req, stream)
     FT_RULE(4, 4); FT_RULE(4, 8); FT_RULE(4, 16); FT_RULE(4, 32);
     FT_RULE(8, 4); FT_RULE(8, 8); FT_RULE(8, 16); FT_RULE(8, 32);
@@ -584,6 +623,19 @@ int launch_decay_rule(const RecurArgs& a, int n_req, cudaStream_t stream) {
 #undef FT_RULE
     FT_REQUIRE(false, "decay rule: no kernel for %d lanes x %d channels", lpc, dpt);
     return -1;
+}
+
+extern "C" int ft_decay_rule(const float* q, const float* k, const float* v, const float* ab, float* o, float* state,
+                             const int* req_start, const int* req_pos0, const int* req_slot, int n_req, int heads, int qk_heads,
+                             int dim, int vd, long long slot_stride, int lanes, int T, void* stream) {
+    FT_REQUIRE(q && k && v && ab && o && state && req_start && req_pos0 && req_slot, "ft_decay_rule: null argument");
+    RecurArgs a;
+    a.q = q; a.k = k; a.v = v; a.ab = ab; a.o = o; a.state = state;
+    a.ldq = a.ldk = qk_heads * dim; a.ldv = a.ldo = heads * vd;
+    a.slot_stride = slot_stride; a.s_off = 0;
+    a.req_start = req_start; a.req_pos0 = req_pos0; a.req_slot = req_slot;
+    a.heads = heads; a.qk_heads = qk_heads; a.dim = dim; a.vd = vd; a.lanes = lanes;
+    return launch_decay_rule(a, n_req, T, (cudaStream_t)stream);
 }
 
 // ------------------------------------------------------------------ gated matrix memory: gates and the running maximum

@@ -754,7 +754,7 @@ static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, 
             launched(2);
         }
         o.ldo = r.ldo;
-        FT_TRY(launch_decay_rule(r, b.n_req, st));
+        FT_TRY(launch_decay_rule(r, b.n_req, T, st));
         FT_TRY(launch_readout(o, T, st));
         launched(2);
     }

@@ -221,8 +221,10 @@ struct RecurArgs {
     long long slot_stride = 0, s_off = 0;
     const int *req_start = nullptr, *req_pos0 = nullptr, *req_slot = nullptr;
     int heads = 0, qk_heads = 0, dim = 0, vd = 0;
+    int lanes = 0;                                // lanes per state column: 4, 8, 16, 32, or 0 = chosen by the launcher
 };
-int launch_decay_rule(const RecurArgs& a, int n_req, cudaStream_t stream);
+// T: tokens of the step, a hint for the choice of lanes
+int launch_decay_rule(const RecurArgs& a, int n_req, int T, cudaStream_t stream);
 
 struct MemoryArgs {                               // gated matrix memory: what precedes the rule
     const float* proj = nullptr;

@@ -113,6 +113,7 @@ SIGNATURES = {
     "ft_add_rmsnorm": (_I, [_VP, _VP, _I, _LL, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _F, _VP]),
     "ft_rope_kv_append": (_I, [_VP, _I, _LL, _VP, _VP, _VP, _VP, _VP, _I, _VP, _VP, _I, _I, _I, _I, _VP]),
     "ft_silu_mul": (_I, [_VP, _I, _LL, _VP, _VP, _I, _I, _VP]),
+    "ft_decay_rule": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _LL, _I, _I, _VP]),
     "ft_attn_decode_scratch_bytes": (_LL, [_I, _I, _I, _I, _I]),
     "ft_attn_decode_default_ctas": (_I, [_I]),
     "ft_debug_attn_trace": (_I, [_VP, _I]),

@@ -455,6 +455,16 @@ int ft_rope_kv_append(const float* qkv, int n_splits, long long split_stride, co
 int ft_silu_mul(const float* gu, int n_splits, long long split_stride, void* act, void* act_lo, int T, int f,
                 void* stream);
 
+/* The scalar-decay rule of the branch mixers alone.  Per request r (rows req_start[r] .. req_start[r+1]-1, in order) and head h:
+ *   S <- ab[t][h][0] * S + ab[t][h][1] * k_t v_t^T,   o_t = S^T q_t
+ * q, k fp32 [T][qk_heads * dim] (head h reads q/k head h / (heads / qk_heads)), v and o fp32 [T][heads * vd], ab fp32
+ * [T][heads][2]; S [dim][vd] of head h lives at state + req_slot[r] * slot_stride + h * dim * vd, is taken as zero when
+ * req_pos0[r] == 0 and is written back.  lanes: lanes that share one state column (4, 8, 16 or 32; 0 = chosen from the
+ * sizes, the grid and T, the number of rows); it changes the order of the sums only. */
+int ft_decay_rule(const float* q, const float* k, const float* v, const float* ab, float* o, float* state,
+                  const int* req_start, const int* req_pos0, const int* req_slot, int n_req, int heads, int qk_heads,
+                  int dim, int vd, long long slot_stride, int lanes, int T, void* stream);
+
 /* K5: paged GQA decode attention, one query token per sequence.  q FP16 [B][nq][d], KV cache FP16,
  * out bf16 [B][nq*d] (+ residual plane out_lo, may be NULL); a sequence with ctx_lens[b] == 0 gets zero rows.  `tile_prefix` (int32 [B+1]) and
  * `scratch` (ft_attn_decode_scratch_bytes) are device work buffers the call fills. */

@@ -481,3 +481,51 @@ def test_served_through_the_handler(tmp_path, monkeypatch):
         h.close()
         runner.shutdown()
         runner.engine.close()
+
+
+# ------------------------------------------------------------------------------------------------ the rule alone
+@pytest.mark.parametrize("lanes", [0, 4, 8, 16, 32])
+@pytest.mark.parametrize("heads,qk_heads,dim,vd", [(3, 3, 20, 9), (4, 2, 64, 33), (2, 1, 128, 16), (1, 1, 7, 70)])
+def test_decay_rule_kernel_alone(lanes, heads, qk_heads, dim, vd):
+    """ft_decay_rule against the recurrence written out: three requests of unequal length in one launch, one of them
+    continuing from a state that its slot already holds, every split of a column over lanes."""
+    from fasttalk_llm_microservice_b200 import build, native
+    build.build()
+    lib = native.load()
+    min_lanes = 4
+    while min_lanes * 32 < dim:
+        min_lanes *= 2
+    if lanes and lanes < min_lanes:
+        pytest.skip("fewer lanes than the channels need")
+    g = torch.Generator().manual_seed(dim * 131 + vd)
+    lens, pos0, slots = [37, 1, 90], [0, 5, 0], [2, 0, 1]
+    T = sum(lens)
+    q, k = torch.randn(T, qk_heads * dim, generator=g) * 0.3, torch.randn(T, qk_heads * dim, generator=g) * 0.3
+    v = torch.randn(T, heads * vd, generator=g)
+    ab = torch.stack([torch.rand(T, heads, generator=g) * 0.5 + 0.5, torch.rand(T, heads, generator=g) * 2.0], -1).contiguous()
+    stride = heads * dim * vd + 4
+    state = torch.randn(3 * stride, generator=g)
+    ref_o = torch.zeros(T, heads * vd, dtype=torch.float64)
+    ref_state = state.double().clone()
+    start = [0, lens[0], lens[0] + lens[1], T]
+    for r in range(3):
+        for h in range(heads):
+            S = ref_state[slots[r] * stride + h * dim * vd:][:dim * vd].reshape(dim, vd).clone()
+            if pos0[r] == 0:
+                S.zero_()
+            gh = h // (heads // qk_heads)
+            for t in range(start[r], start[r + 1]):
+                S = ab[t, h, 0].double() * S + ab[t, h, 1].double() * torch.outer(k[t, gh * dim:(gh + 1) * dim].double(), v[t, h * vd:(h + 1) * vd].double())
+                ref_o[t, h * vd:(h + 1) * vd] = S.T @ q[t, gh * dim:(gh + 1) * dim].double()
+            ref_state[slots[r] * stride + h * dim * vd:][:dim * vd] = S.reshape(-1)
+    dev = "cuda"
+    dq, dk, dv, dab, dst = q.to(dev), k.to(dev), v.to(dev), ab.to(dev), state.to(dev)
+    o = torch.zeros(T, heads * vd, device=dev)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    rs, rp, sl = i32(start), i32(pos0), i32(slots)
+    rc = lib.ft_decay_rule(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dab.data_ptr(), o.data_ptr(), dst.data_ptr(), rs.data_ptr(),
+                           rp.data_ptr(), sl.data_ptr(), 3, heads, qk_heads, dim, vd, stride, lanes, T, None)
+    torch.cuda.synchronize()
+    assert rc == 0, native.last_error()
+    assert rel(o.cpu().double().numpy(), ref_o.numpy()) < 1e-5
+    assert rel(dst.cpu().double().numpy(), ref_state.numpy()) < 1e-5
