@@ -466,28 +466,50 @@ __device__ __forceinline__ void cp_async_f32(float* dst_smem, const float* src) 
 __device__ __forceinline__ void cp_async_f32x4(float* dst_smem, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
 }
-// VEC: keys and queries are copied 16 bytes at a time (dim a multiple of 4, rows and bases on 16-byte boundaries)
-template <int LPC, int DPT, bool VEC>
+// VEC: keys and queries are copied 16 bytes at a time (dim a multiple of 4, rows and bases on 16-byte boundaries).
+// CPT: state columns per thread.  A thread reads its run of key and query channels once per token and uses it for all of
+// its CPT columns — the shared-memory reads, not the arithmetic, bound the kernel with one column per thread (every one of
+// a column's 128 / LPC sibling columns in the CTA reads the same runs again).  The CPT partial read-outs are summed over the
+// LPC lanes by halving: in each of the first log2(CPT) steps a lane hands half of its columns to its partner and keeps the
+// other half, afterwards every lane holds one column and the tree goes on as usual.
+template <int LPC, int DPT, int CPT, bool VEC>
 __global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
-    constexpr int VB = RTHREADS / LPC, RUN = DPT + 4, DP = LPC * RUN;
+    constexpr int VB = RTHREADS / LPC * CPT, RUN = DPT + 4, DP = LPC * RUN;
     constexpr int BUF = 2 * RCH * DP + RCH * VB + RCH * 2;      // floats of one staged chunk: keys | queries | values | (a, b)
     constexpr int NST = rule_stages(DP);
     extern __shared__ __align__(16) float rs[];
     const int r = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * VB;
-    const int s = threadIdx.x % LPC, jl = threadIdx.x / LPC, j = j0 + jl;
+    const int s = threadIdx.x % LPC, jl = threadIdx.x / LPC, j = j0 + jl * CPT;      // the thread's first column
     const int t0 = a.req_start[r], t1 = a.req_start[r + 1];
     if (t1 <= t0) return;
     const int gh = h / (a.heads / a.qk_heads);
     float* S = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.s_off + (size_t)h * a.dim * a.vd;
-    const bool live = j < a.vd;
     if (LPC * DPT != a.dim || j0 + VB > a.vd)                                  // the padding stays zero from here on
         for (int i = threadIdx.x; i < NST * BUF; i += RTHREADS) rs[i] = 0.f;
-    f32x2 st[DPT / 2];                       // channels (2 i, 2 i + 1) of the lane's run
+    f32x2 st[CPT][DPT / 2];                  // per column: channels (2 i, 2 i + 1) of the lane's run
+    const bool old = a.req_pos0[r] > 0;
+    // four columns of a row are 16 bytes of the state when vd is a multiple of 4 (slots and heads then start on 16 bytes)
+    const bool wide = CPT == 4 && (a.vd & 3) == 0 && (((uintptr_t)S) & 15) == 0;
+    if (wide) {
 #pragma unroll
-    for (int i = 0; i < DPT; i += 2) {
-        const int d = s * DPT + i;
-        const bool old = a.req_pos0[r] > 0 && live;
-        st[i / 2] = pack2(old && d < a.dim ? S[(size_t)d * a.vd + j] : 0.f, old && d + 1 < a.dim ? S[(size_t)(d + 1) * a.vd + j] : 0.f);
+        for (int i = 0; i < DPT; i += 2) {
+            const int d = s * DPT + i;
+            float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+            if (old && j < a.vd && d < a.dim) lo = *reinterpret_cast<const float4*>(S + (size_t)d * a.vd + j);
+            if (old && j < a.vd && d + 1 < a.dim) hi = *reinterpret_cast<const float4*>(S + (size_t)(d + 1) * a.vd + j);
+            const float l4[4] = {lo.x, lo.y, lo.z, lo.w}, h4[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) st[c][i / 2] = pack2(l4[c], h4[c]);
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < CPT; ++c)
+#pragma unroll
+            for (int i = 0; i < DPT; i += 2) {
+                const int d = s * DPT + i;
+                const bool in = old && j + c < a.vd;
+                st[c][i / 2] = pack2(in && d < a.dim ? S[(size_t)d * a.vd + j + c] : 0.f, in && d + 1 < a.dim ? S[(size_t)(d + 1) * a.vd + j + c] : 0.f);
+            }
     }
     __syncthreads();
     auto stage = [&](int buf, int c0) {          // always commits a group, an empty one past the end: the count stays uniform
@@ -535,93 +557,162 @@ __global__ void __launch_bounds__(RTHREADS) decay_rule_kernel(RecurArgs a) {
         const float* sq = sk + RCH * DP;
         const float* sv = sq + RCH * DP;
         const float* sab = sv + RCH * VB;
-        auto token = [&](int tt) {
-            const float da = sab[2 * tt], bv = sab[2 * tt + 1] * sv[tt * VB + jl];
-            const f32x2 da2 = pack2(da, da), bv2 = pack2(bv, bv);
+        // update: the token's state update and each column's partial read-out over the lane's run
+        auto update = [&](int tt, float* o) {
+            const float da = sab[2 * tt], db = sab[2 * tt + 1];
+            const f32x2 da2 = pack2(da, da);
+            f32x2 kk[DPT / 2], qq[DPT / 2];
             const ulonglong2* kp = reinterpret_cast<const ulonglong2*>(sk + tt * DP + s * RUN);
             const ulonglong2* qp = reinterpret_cast<const ulonglong2*>(sq + tt * DP + s * RUN);
-            f32x2 o0 = 0ull, o1 = 0ull;
 #pragma unroll
             for (int i = 0; i < DPT / 4; ++i) {
                 const ulonglong2 kv = kp[i], qv = qp[i];
-                st[2 * i] = fma2(da2, st[2 * i], mul2(bv2, kv.x));
-                st[2 * i + 1] = fma2(da2, st[2 * i + 1], mul2(bv2, kv.y));
-                o0 = fma2(st[2 * i], qv.x, o0);
-                o1 = fma2(st[2 * i + 1], qv.y, o1);
+                kk[2 * i] = kv.x; kk[2 * i + 1] = kv.y;
+                qq[2 * i] = qv.x; qq[2 * i + 1] = qv.y;
             }
-            float p0, p1, p2, p3;
-            unpack2(o0, p0, p1);
-            unpack2(o1, p2, p3);
-            float o = (p0 + p2) + (p1 + p3);
 #pragma unroll
-            for (int off = LPC / 2; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-            if (s == 0 && live) a.o[(size_t)(c0 + tt) * a.ldo + (size_t)h * a.vd + j] = o;
+            for (int c = 0; c < CPT; ++c) {
+                const float bv = db * sv[tt * VB + jl * CPT + c];
+                const f32x2 bv2 = pack2(bv, bv);
+                f32x2 o0 = 0ull, o1 = 0ull;
+#pragma unroll
+                for (int i = 0; i < DPT / 2; i += 2) {
+                    st[c][i] = fma2(da2, st[c][i], mul2(bv2, kk[i]));
+                    st[c][i + 1] = fma2(da2, st[c][i + 1], mul2(bv2, kk[i + 1]));
+                    o0 = fma2(st[c][i], qq[i], o0);
+                    o1 = fma2(st[c][i + 1], qq[i + 1], o1);
+                }
+                float p0, p1, p2, p3;
+                unpack2(o0, p0, p1);
+                unpack2(o1, p2, p3);
+                o[c] = (p0 + p2) + (p1 + p3);
+            }
+        };
+        // finish: sum over the LPC lanes; the column a lane ends up with is made of the lane bits used in the halving steps.
+        // Taken for four tokens at a time, so that the shuffle chains of the four overlap instead of stalling the warp.
+        auto finish = [&](int tt, const float* o) {
+            int col = 0;
+            float v = o[0];
+            if (CPT == 4) {
+                const bool up = (s & (LPC / 2)) != 0, up2 = (s & (LPC / 4)) != 0;
+                const float g0 = __shfl_xor_sync(0xffffffffu, up ? o[0] : o[2], LPC / 2);
+                const float g1 = __shfl_xor_sync(0xffffffffu, up ? o[1] : o[3], LPC / 2);
+                const float k0 = (up ? o[2] : o[0]) + g0, k1 = (up ? o[3] : o[1]) + g1;
+                const float g2 = __shfl_xor_sync(0xffffffffu, up2 ? k0 : k1, LPC / 4);
+                v = (up2 ? k1 : k0) + g2;
+                col = (up ? 2 : 0) + (up2 ? 1 : 0);
+#pragma unroll
+                for (int off = LPC / 8; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+            } else if (CPT == 2) {
+                const bool up = (s & (LPC / 2)) != 0;
+                const float g0 = __shfl_xor_sync(0xffffffffu, up ? o[0] : o[1], LPC / 2);
+                v = (up ? o[1] : o[0]) + g0;
+                col = up ? 1 : 0;
+#pragma unroll
+                for (int off = LPC / 4; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+            } else {
+#pragma unroll
+                for (int off = LPC / 2; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+            }
+            if ((s & (LPC / CPT - 1)) == 0 && j + col < a.vd) a.o[(size_t)(c0 + tt) * a.ldo + (size_t)h * a.vd + j + col] = v;
         };
         if (nt == RCH) {
-#pragma unroll 8
-            for (int tt = 0; tt < RCH; ++tt) token(tt);
+#pragma unroll 1
+            for (int t4 = 0; t4 < RCH; t4 += 4) {
+                float o[4][CPT];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) update(t4 + x, o[x]);
+#pragma unroll
+                for (int x = 0; x < 4; ++x) finish(t4 + x, o[x]);
+            }
         } else {
-            for (int tt = 0; tt < nt; ++tt) token(tt);
+            for (int tt = 0; tt < nt; ++tt) {
+                float o[CPT];
+                update(tt, o);
+                finish(tt, o);
+            }
         }
         __syncthreads();
     }
-    if (live) {
+    if (wide) {
+#pragma unroll
+        for (int i = 0; i < DPT; i += 2) {
+            const int d = s * DPT + i;
+            float l4[4], h4[4];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) unpack2(st[c][i / 2], l4[c], h4[c]);
+            if (j < a.vd && d < a.dim) *reinterpret_cast<float4*>(S + (size_t)d * a.vd + j) = make_float4(l4[0], l4[1], l4[2], l4[3]);
+            if (j < a.vd && d + 1 < a.dim) *reinterpret_cast<float4*>(S + (size_t)(d + 1) * a.vd + j) = make_float4(h4[0], h4[1], h4[2], h4[3]);
+        }
+        return;
+    }
+#pragma unroll
+    for (int c = 0; c < CPT; ++c)
 #pragma unroll
         for (int i = 0; i < DPT; i += 2) {
             const int d = s * DPT + i;
             float lo, hi;
-            unpack2(st[i / 2], lo, hi);
-            if (d < a.dim) S[(size_t)d * a.vd + j] = lo;
-            if (d + 1 < a.dim) S[(size_t)(d + 1) * a.vd + j] = hi;
+            unpack2(st[c][i / 2], lo, hi);
+            if (j + c < a.vd && d < a.dim) S[(size_t)d * a.vd + j + c] = lo;
+            if (j + c < a.vd && d + 1 < a.dim) S[(size_t)(d + 1) * a.vd + j + c] = hi;
         }
-    }
 }
 
-template <int LPC, int DPT>
+template <int LPC, int DPT, int CPT>
 static int launch_decay_rule_t(const RecurArgs& a, int n_req, cudaStream_t stream) {
-    constexpr int VB = RTHREADS / LPC, DP = LPC * (DPT + 4);
+    constexpr int VB = RTHREADS / LPC * CPT, DP = LPC * (DPT + 4);
     const size_t smem = (size_t)rule_stages(DP) * (2 * RCH * DP + RCH * VB + RCH * 2) * 4;
     const bool vec = (a.dim & 3) == 0 && (a.ldk & 3) == 0 && (a.ldq & 3) == 0 && ((uintptr_t)a.k & 15) == 0 && ((uintptr_t)a.q & 15) == 0;
     if (smem > 48 * 1024) {
-        FT_CHECK_CUDA(cudaFuncSetAttribute(decay_rule_kernel<LPC, DPT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        FT_CHECK_CUDA(cudaFuncSetAttribute(decay_rule_kernel<LPC, DPT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FT_CHECK_CUDA(cudaFuncSetAttribute(decay_rule_kernel<LPC, DPT, CPT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FT_CHECK_CUDA(cudaFuncSetAttribute(decay_rule_kernel<LPC, DPT, CPT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }
     dim3 grid((a.vd + VB - 1) / VB, a.heads, n_req);
-    if (vec) decay_rule_kernel<LPC, DPT, true><<<grid, RTHREADS, smem, stream>>>(a);
-    else decay_rule_kernel<LPC, DPT, false><<<grid, RTHREADS, smem, stream>>>(a);
+    if (vec) decay_rule_kernel<LPC, DPT, CPT, true><<<grid, RTHREADS, smem, stream>>>(a);
+    else decay_rule_kernel<LPC, DPT, CPT, false><<<grid, RTHREADS, smem, stream>>>(a);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
 
-// Lanes per column and channels per lane: the fewest lanes whose runs (<= 32 channels) cover dim — the widest column
-// blocks and the best-coalesced state traffic, what a step of single tokens wants — and more lanes with shorter runs for
-// prompt portions and while the grid would leave most of the GPU idle.  The split changes the order of a sum, nothing else.
-// T: tokens in the step (only a hint for that choice).
+// Lanes per column (LPC), channels per lane (DPT <= 16, 32 only beyond 512 channels) and columns per thread (CPT): the
+// fewest lanes whose runs cover dim and four columns per thread — the widest column blocks, the best-coalesced state
+// traffic and the fewest shared-memory reads per multiply-add; then, while fewer than 96 CTAs would run (one long prompt
+// with few heads): two columns per thread, more lanes with shorter runs, at last one column (measured order).  The split
+// changes the order of a sum, nothing else.  a.lanes fixes LPC.  T: tokens in the step (unused by the present rule, kept
+// for callers that tune).
 int launch_decay_rule(const RecurArgs& a, int n_req, int T, cudaStream_t stream) {
+    (void)T;
     FT_REQUIRE(a.heads >= 1 && a.qk_heads >= 1 && a.heads % a.qk_heads == 0 && a.dim >= 1 && a.dim <= 1024 && a.vd >= 1,
                "decay rule: bad sizes (heads %d, key heads %d, dim %d, values %d)", a.heads, a.qk_heads, a.dim, a.vd);
     if (n_req <= 0) return 0;
     int lpc = 4, dpt = 4;
-    while (dpt < 32 && lpc * dpt < a.dim) dpt *= 2;
-    while (lpc * dpt < a.dim) lpc *= 2;
-    auto ctas = [&](int l) { return (long long)n_req * a.heads * ((a.vd + RTHREADS / l - 1) / (RTHREADS / l)); };
+    while (dpt < 16 && lpc * dpt < a.dim) dpt *= 2;
+    while (lpc < 32 && lpc * dpt < a.dim) lpc *= 2;
+    if (lpc * dpt < a.dim) dpt = 32;
+    int cpt = dpt == 32 ? 2 : 4;
+    auto ctas = [&](int l, int c) { return (long long)n_req * a.heads * ((a.vd + RTHREADS / l * c - 1) / (RTHREADS / l * c)); };
     if (a.lanes > 0) {
         FT_REQUIRE((a.lanes == 4 || a.lanes == 8 || a.lanes == 16 || a.lanes == 32) && a.lanes >= lpc,
                    "decay rule: %d lanes per column do not hold %d channels", a.lanes, a.dim);
         while (lpc < a.lanes && dpt > 4) { lpc *= 2; dpt /= 2; }
+        cpt = dpt == 32 ? 2 : 4;
+        while (cpt > 1 && ctas(lpc, cpt) < 96) cpt /= 2;
     } else {
-        // prompt portions (many tokens per request): runs of at most 16 channels keep a token's arithmetic short; then
-        // more lanes while less than one CTA per SM would run
-        if (T >= 32 * n_req && lpc < 32 && dpt > 16) { lpc *= 2; dpt /= 2; }
-        while (lpc < 32 && dpt > 8 && ctas(lpc) < 96) { lpc *= 2; dpt /= 2; }
+        while (ctas(lpc, cpt) < 96) {
+            if (cpt > 2) cpt = 2;
+            else if (lpc < 32 && dpt > 4) { lpc *= 2; dpt /= 2; }
+            else if (cpt > 1) cpt = 1;
+            else break;
+        }
     }
-#define FT_RULE(L, D) if (lpc == L && dpt == D) return launch_decay_rule_t<L, D>(a, n_req, stream)
-    FT_RULE(4, 4); FT_RULE(4, 8); FT_RULE(4, 16); FT_RULE(4, 32);
-    FT_RULE(8, 4); FT_RULE(8, 8); FT_RULE(8, 16); FT_RULE(8, 32);
-    FT_RULE(16, 4); FT_RULE(16, 8); FT_RULE(16, 16); FT_RULE(16, 32);
-    FT_RULE(32, 4); FT_RULE(32, 8); FT_RULE(32, 16); FT_RULE(32, 32);
+#define FT_RULE(L, D, C) if (lpc == L && dpt == D && cpt == C) return launch_decay_rule_t<L, D, C>(a, n_req, stream)
+#define FT_RULE_L(L) FT_RULE(L, 4, 1); FT_RULE(L, 4, 2); FT_RULE(L, 4, 4); FT_RULE(L, 8, 1); FT_RULE(L, 8, 2); FT_RULE(L, 8, 4); \
+                     FT_RULE(L, 16, 1); FT_RULE(L, 16, 2); FT_RULE(L, 16, 4)
+    FT_RULE_L(4); FT_RULE_L(8); FT_RULE_L(16); FT_RULE_L(32);
+    FT_RULE(32, 32, 1); FT_RULE(32, 32, 2);
+#undef FT_RULE_L
 #undef FT_RULE
-    FT_REQUIRE(false, "decay rule: no kernel for %d lanes x %d channels", lpc, dpt);
+    FT_REQUIRE(false, "decay rule: no kernel for %d lanes x %d channels x %d columns", lpc, dpt, cpt);
     return -1;
 }
 
