@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs 
     float* sm = sq + ((a.dim + 3) & ~3);               // [warps] running maxima
     float* sl = sm + kWinWarps;                        // [warps] running sums
     float* sacc = sl + kWinWarps;                      // [warps][vdim]
-    const int h = blockIdx.x, t = blockIdx.y;
+    const int h = blockIdx.y, t = blockIdx.x;      // tokens along x: a step may hold more rows than y allows
     const int g = h / (a.H / a.G);
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p = a.positions[t];
@@ -386,7 +386,7 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
 // portions that follow them run on the tiled kernel when the head sizes allow it (multiples of 4, at most 64 query heads
 // per key head), otherwise like the single tokens.
 int launch_window_attention(const WindowArgs& a, int T, int n_single, const WindowTiles& tm, cudaStream_t stream) {
-    FT_REQUIRE(a.H >= 1 && a.G >= 1 && a.H % a.G == 0 && a.dim >= 1 && a.vdim >= 1 && a.vdim <= 256,
+    FT_REQUIRE(a.H >= 1 && a.G >= 1 && a.H % a.G == 0 && a.dim >= 1 && a.vdim >= 1 && a.vdim <= 512,
                "window attention: bad head sizes (heads %d, kv heads %d, dim %d, vdim %d)", a.H, a.G, a.dim, a.vdim);
     FT_REQUIRE(a.rot_dims >= 0 && a.rot_dims <= a.dim && (a.rot_dims & 1) == 0 && (a.rot_dims == 0 || (a.dim & 1) == 0),
                "window attention: rotary pairs need even sizes (dim %d, rotated %d)", a.dim, a.rot_dims);
@@ -395,7 +395,7 @@ int launch_window_attention(const WindowArgs& a, int T, int n_single, const Wind
     FT_CHECK_CUDA(cudaGetLastError());
     const int grp = a.H / a.G;
     const size_t tsm = (size_t)((WT_ROWS + WT_KEYS) * (a.dim + 4) + WT_KEYS * a.vdim + WT_ROWS * (WT_KEYS + 1) + WT_ROWS) * 4;
-    const bool tiled = tm.n_tiles > 0 && (a.dim & 3) == 0 && (a.vdim & 3) == 0 && grp <= WT_ROWS && tsm <= 200 * 1024;
+    const bool tiled = tm.n_tiles > 0 && (a.dim & 3) == 0 && (a.vdim & 3) == 0 && grp <= WT_ROWS && a.vdim <= 256 && tsm <= 200 * 1024;
     int rows_each = T;                                 // rows of the one-CTA-per-(token, head) kernel
     if (tiled) {
         rows_each = n_single;
@@ -414,7 +414,7 @@ int launch_window_attention(const WindowArgs& a, int T, int n_single, const Wind
     T = rows_each;
     const size_t smem = (size_t)(((a.dim + 3) & ~3) + 2 * kWinWarps + kWinWarps * a.vdim) * 4;
     const bool vec = (a.dim & 3) == 0 && (a.vdim & 3) == 0;      // every key row then starts on 16 bytes
-    dim3 grid(a.H, T);
+    dim3 grid(T, a.H);
     const int vpl = (a.vdim + 31) / 32;
 #define FT_WIN(V)                                                                                   \
     do {                                                                                            \
@@ -424,7 +424,8 @@ int launch_window_attention(const WindowArgs& a, int T, int n_single, const Wind
     if (vpl <= 1) FT_WIN(1);
     else if (vpl <= 2) FT_WIN(2);
     else if (vpl <= 4) FT_WIN(4);
-    else FT_WIN(8);
+    else if (vpl <= 8) FT_WIN(8);
+    else FT_WIN(16);
 #undef FT_WIN
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;

@@ -174,9 +174,11 @@ int ft_debug_prefill_logits(ft_engine* e, const int* tokens, int n_tokens, int c
 
 /* ------------------------------------------------------------------------------------------
  * Layered models — decoders described layer by layer instead of by the Llama field set above: each layer names
- * its token mixer (latent attention over a paged latent cache, or a gated delta rule with per-channel decay whose
- * state lives in a per-session slot) and its feed-forward (none, or a mixture of experts with group-limited
- * routing).  Every size is a run-time value.  The engine around them is the same one: page allocator, session
+ * its form (how its sublayers join the stream), its token mixer (latent attention over a paged latent cache; a gated
+ * delta rule with per-channel decay whose state lives in a per-session slot; or one or two branch mixers side by side:
+ * sliding-window attention over a paged key / value cache, and three linear recurrences with a scalar decay per head
+ * and token whose matrix states live in the slot) and its feed-forward (none, dense, or a mixture of experts with
+ * softmax or sigmoid routing).  Every size is a run-time value.  The engine around them is the same one: page allocator, session
  * table, continuous-batching scheduler, sampling, stepping thread.  No counterpart in the reference, which names
  * models by tag and owns no model code (app/utils/config.py:86).
  *

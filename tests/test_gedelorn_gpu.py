@@ -122,13 +122,14 @@ MIXED = [layer(space(), dense()), layer(parallel(), moe()), layer(memory(), dens
     [layer(parallel(window(heads=4, kv_heads=4, dim=10, size=1, rot=(10, 100.0), softcap=0), decaying(heads=2, dim=4, vdim=70, decay=(1.0, 0.5))))],
     [layer(parallel(window(heads=3, kv_heads=1, dim=36, size=400, rot=None), left_scale=1.0, right_scale=0.25))],
     [layer(parallel(window(heads=2, kv_heads=1, dim=160, size=90, rot=(64, 1e4), scale=0.08), decaying(heads=1, dim=300, vdim=8, decay=(0.97,))))],
+    [layer(parallel(window(heads=1, kv_heads=1, dim=264, size=50, rot=(8, 1e4), scale=0.06), decaying(heads=1, dim=8, vdim=8, decay=(0.9,))))],
     [layer(space(), dense())],
     [layer(memory(), moe())],
     [layer(memory(), moe(experts=3, top=3, shared=0))],                  # every expert chosen, no shared expert
     [layer(memory(), moe(experts=40, top=1, scale=None, shared=9))],     # more experts than lanes, one chosen
     MIXED,
 ], ids=["memory", "memory-1head", "memory-wide", "space", "space-1group-1tap", "space-big-state", "parallel", "parallel-window1",
-        "parallel-norot", "parallel-wide-heads", "dense", "moe", "moe-all", "moe-top1", "mixed"])
+        "parallel-norot", "parallel-wide-heads", "parallel-widest-head", "dense", "moe", "moe-all", "moe-top1", "mixed"])
 def test_whole_prompt_matches_oracle(layers):
     spec, w = make(layers, seed=3)
     eng = engine(spec, w)
